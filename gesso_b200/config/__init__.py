@@ -6,10 +6,11 @@ from .registry import (architecture_name, known_architectures, parse_strict_json
 from .lfm2 import Lfm2Config, effective_ff_dim
 from .sodurax import SoduraxConfig
 from .memipel import MemipelConfig
+from .mabidra import MabidraConfig
 
 __all__ = [
     "BlockSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule",
     "architecture_name", "known_architectures", "parse_strict_json", "read_config",
     "register_architecture", "spec_from_config", "spec_from_dir", "unregister_architecture",
-    "Lfm2Config", "effective_ff_dim", "SoduraxConfig", "MemipelConfig",
+    "Lfm2Config", "effective_ff_dim", "SoduraxConfig", "MemipelConfig", "MabidraConfig",
 ]

@@ -57,11 +57,16 @@ class ScheduleEntry:
 
     ``layer`` indexes ``ModelSpec.blocks``.  ``cache_of`` is ``None`` when the
     entry owns a cache of its own, or the index (into the schedule) of an
-    earlier entry whose cache this entry reads without writing.
+    earlier entry whose cache this entry reads without writing.  A layer that is
+    named by several entries runs with the same tensors, each time on a cache of
+    the entry's own.
     """
 
     layer: int
     cache_of: Optional[int] = None
+    # what happens to the residual stream right before this entry's layer: ``(index into
+    # ModelSpec.stream_parts, argument)``, e.g. the re-entry mix of a looped stack with the number of the pass
+    before: Optional[Tuple[int, Any]] = None
 
 
 @dataclass(frozen=True)
@@ -73,6 +78,9 @@ class ModelSpec:
     schedule: Tuple[ScheduleEntry, ...]
     final_norm: PartSpec
     tie_embedding: bool
+    # parts that act on the residual stream between layers (registered "stream" kinds), each with the
+    # internal name prefix of its tensors; schedule entries call them through ``ScheduleEntry.before``
+    stream_parts: Tuple[Tuple[str, PartSpec], ...] = ()
     embedding_scale: float = 1.0
     # logits = softcap * tanh(logit_scale * logits / softcap); no cap when None (LFM2 has neither)
     logit_scale: float = 1.0

@@ -6,6 +6,7 @@
 //                   out = g * sigmoid(alpha * g) * (u + 1)                  [N, F]
 //               Plain layout: columns [0, F) are the gate projection, [F, 2F) the up projection.  Packed layout:
 //               every group of 16 columns holds 8 gate columns and then the matching 8 up columns.
+// xielu:        see below.
 #include <math.h>
 
 #include "common.cuh"
@@ -62,6 +63,37 @@ GESSO_API int gesso_glu_clamped(const void* gu, void* out, int dtype, int n_rows
     else if (dtype == GESSO_BF16)
         launch_pdl(glu_clamped_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out,
                    (long long)n_rows, F, packed, limit, alpha);
+    else
+        return GESSO_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+// xielu: a piecewise activation with two learned numbers p and q (read from device memory, so that a step never
+// waits for the host):
+//     z > 0:   softplus(p) z^2 + z / 2
+//     z <= 0:  (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+__device__ __forceinline__ float softplus_f(float a) { return fmaxf(a, 0.f) + log1pf(expf(-fabsf(a))); }
+
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ x, T* __restrict__ out, long long n, const float* __restrict__ pq) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float sp = softplus_f(pq[0]), sq = 0.5f + softplus_f(pq[1]);
+    const float z = to_f32(x[i]);
+    const float y = z > 0.f ? fmaf(sp * z, z, 0.5f * z) : fmaf(sq, expm1f(z) - z, 0.5f * z);
+    out[i] = from_f32<T>(y);
+}
+
+GESSO_API int gesso_xielu(const void* x, void* out, int dtype, long long n, const float* pq, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 2147483647LL) return GESSO_ERR_BAD_SIZE;
+    if (dtype == GESSO_F32)
+        launch_pdl(xielu_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)x, (float*)out, n, pq);
+    else if (dtype == GESSO_BF16)
+        launch_pdl(xielu_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, n, pq);
     else
         return GESSO_ERR_BAD_DTYPE;
     return launch_status();

@@ -33,7 +33,7 @@ _SIGNATURES = {
     "gesso_qk_norm_rope_store": [P, I, P, P, F, P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, P, P, I, I, P],
     "gesso_paged_attention_generic": [P, P, P, I, P, I, I, P, P, P, I, I, I, I, I, F, I, I, P, I, I, P, P, I, P],
     "gesso_add_dyt": [P, P, I, P, F, P, P, F, P, P, P, I, P, I, I, P],
-    "gesso_moe_route": [P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "gesso_moe_route": [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "gesso_moe_pair_up": [P, I, P, I, P, P, I, I, I, I, I, F, I, P],
     "gesso_moe_pair_down": [P, I, P, I, P, P, P, I, I, I, I, I, P],
     "gesso_swiglu": [P, P, I, I, I, I, P],

@@ -3,7 +3,9 @@
 // Router (one warp per token, all float32).  The logits z = W_router x come from a matrix product with float32
 // accumulation (bfloat16 operands are exact in it, so a bfloat16 run's logits are the float32 sums of the same
 // numbers); this kernel does the rest:
-//   s_e = score(z_e)  (sigmoid, or softmax over the experts),
+//   z_e += logit_bias[e] (optional),
+//   s_e = score(z_e)  (sigmoid, softmax over the experts, or z_e itself for weights that are the softmax over
+//   the CHOSEN experts' logits only),
 //   c_e = s_e + correction[e]                  (the score an expert is CHOSEN by; the weight uses s_e),
 //   experts form `n_groups` equal groups of neighbours; a group's score is the sum of its `group_top`
 //   largest c_e; only experts of the `keep_groups` best groups can be chosen (the others' c_e count as
@@ -27,7 +29,7 @@
 
 #include "common.cuh"
 
-enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1 };
+enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1, MOE_SCORE_SOFTMAX_CHOSEN = 2 };
 enum { MOE_ACT_RELU2 = 0, MOE_ACT_SILU = 1, MOE_ACT_GELU_TANH = 2, MOE_ACT_GLU_CLAMPED = 3 };
 #define MOE_GLU_ALPHA 1.702f
 
@@ -38,8 +40,8 @@ __device__ __forceinline__ float moe_act(float v, int act) {
 }
 
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
-                 int* __restrict__ top_idx, float* __restrict__ top_w, int n_tokens, int E, int top,
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ logit_bias,
+                 const float* __restrict__ correction, int* __restrict__ top_idx, float* __restrict__ top_w, int n_tokens, int E, int top,
                  int n_groups, int keep_groups, int group_top, int score_fn, int renorm, float weight_scale) {
     extern __shared__ float moe_smem[];
     pdl_launch_dependents();
@@ -50,7 +52,7 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
     float* s = moe_smem + (size_t)wid * (2 * E + n_groups);   // scores
     float* c = s + E;                                           // choice scores (-inf once taken or shut out)
     float* gs = c + E;                                          // group scores
-    for (int e = lane; e < E; e += 32) s[e] = logits[(size_t)t * E + e];
+    for (int e = lane; e < E; e += 32) s[e] = logits[(size_t)t * E + e] + (logit_bias ? logit_bias[e] : 0.f);
     __syncwarp();
     if (score_fn == MOE_SCORE_SOFTMAX) {
         float m = -INFINITY;
@@ -60,9 +62,9 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
         for (int e = lane; e < E; e += 32) sum += expf(s[e] - m);
         sum = warp_sum(sum);
         for (int e = lane; e < E; e += 32) s[e] = expf(s[e] - m) / sum;
-    } else {
+    } else if (score_fn == MOE_SCORE_SIGMOID) {
         for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-s[e]));
-    }
+    }                                                // MOE_SCORE_SOFTMAX_CHOSEN: the logits themselves
     __syncwarp();
     for (int e = lane; e < E; e += 32) c[e] = s[e] + (correction ? correction[e] : 0.f);
     __syncwarp();
@@ -120,6 +122,14 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
         }
         __syncwarp();
     }
+    if (score_fn == MOE_SCORE_SOFTMAX_CHOSEN) {      // softmax over the chosen experts' logits, nothing else
+        const float z = lane < top ? top_w[(size_t)t * top + lane] : -INFINITY;
+        const float m = warp_max(z);
+        const float ex = lane < top ? expf(z - m) : 0.f;
+        const float sum = warp_sum(ex);
+        if (lane < top) top_w[(size_t)t * top + lane] = ex / sum * weight_scale;
+        return;
+    }
     if (lane < top) {
         float w = top_w[(size_t)t * top + lane];
         if (renorm) w /= wsum;
@@ -127,8 +137,8 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
     }
 }
 
-// logits [tokens, E] and correction [E] (or null) float32; top_idx / top_w [tokens, top].
-GESSO_API int gesso_moe_route(const float* logits, const float* correction, int* top_idx,
+// logits [tokens, E], logit_bias [E] (or null) and correction [E] (or null) float32; top_idx / top_w [tokens, top].
+GESSO_API int gesso_moe_route(const float* logits, const float* logit_bias, const float* correction, int* top_idx,
                               float* top_w, int n_tokens, int E, int top, int n_groups, int keep_groups,
                               int group_top, int score_fn, int renorm, float weight_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
@@ -138,7 +148,7 @@ GESSO_API int gesso_moe_route(const float* logits, const float* correction, int*
     const size_t smem = (size_t)4 * (2 * E + n_groups) * sizeof(float);
     if (smem > 48 * 1024) return GESSO_ERR_BAD_SIZE;
     const dim3 grid((n_tokens + 3) / 4);
-    launch_pdl(moe_route_kernel, grid, dim3(128), smem, stream, logits, correction, top_idx, top_w, n_tokens, E, top,
+    launch_pdl(moe_route_kernel, grid, dim3(128), smem, stream, logits, logit_bias, correction, top_idx, top_w, n_tokens, E, top,
                n_groups, keep_groups, group_top, score_fn, renorm, weight_scale);
     return launch_status();
 }

@@ -61,3 +61,11 @@ def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=
                                      split_weights, slopes=slopes, sink=sink)
     return ops.paged_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table,
                                        ctx.positions, ctx.seg_of_token, window, scale, keep_first, gate)
+
+
+def sigmoid_attention(rt, q, cache, ctx, scale, dist_bias=None, temp_coef: float = 0.0, temp_every: int = 0, gate=None,
+                      window=None):
+    """Attention with sigmoid weights (no softmax) of the step's queries over the paged cache.  float32 runs and
+    sizes the tensor-core kernels do not take run the FP32-arithmetic kernel."""
+    return ops.sigmoid_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
+                                         ctx.seg_of_token, scale, dist_bias, temp_coef, temp_every, gate, window)

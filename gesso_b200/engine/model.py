@@ -7,7 +7,9 @@ engine hands it a :class:`~gesso_b200.engine.batch.StepContext` and per-entry ca
 Forward of one step (src/Inference/Inference.jl:2358-2521 is the reference's per-pass loop)::
 
     h = embedding[token_ids]                      (float32 residual stream)
-    for entry in schedule:  pending = block(h, pending, ctx, cache_view(entry))
+    for entry in schedule:
+        h, pending = stream_part(h, pending, ctx, argument)       (entries that name one in ``before``)
+        pending = block(h, pending, ctx, cache_view(entry))
     logits = lm_head( final_norm(h + pending)[wanted rows] )      (then the spec's logit scale / soft cap, if any)
 """
 from __future__ import annotations
@@ -22,7 +24,7 @@ from ..cache.manager import PagedGroupSpec
 from ..config.spec import ModelSpec
 from ..errors import invalid
 from ..parts.base import PagedNeed, ParamDecl, StateNeed
-from ..parts.registry import build_block, build_norm
+from ..parts.registry import build_block, build_norm, build_stream
 from ..weights.loader import model_param_decls, place_tensor
 
 
@@ -43,6 +45,13 @@ class Runtime:
         from . import attention_dispatch
         return attention_dispatch.paged_attention(self, q, cache, ctx, window, scale, keep_first, gate, split_weights,
                                                   sink=sink, slopes=slopes, values_are_keys=values_are_keys)
+
+    def sigmoid_attention(self, q, cache, ctx, scale, dist_bias=None, temp_coef: float = 0.0, temp_every: int = 0,
+                          gate=None, window=None):
+        """Attention with sigmoid weights of the step's queries over the paged cache (kernel choice lives here)."""
+        from . import attention_dispatch
+        return attention_dispatch.sigmoid_attention(self, q, cache, ctx, scale, dist_bias, temp_coef, temp_every, gate,
+                                                    window)
 
 
 @dataclass
@@ -155,13 +164,23 @@ class Model:
         self.blocks = [build_block(b) for b in spec.blocks]
         for b, blk in zip(spec.blocks, self.blocks):
             blk.bind({k[len(b.prefix):]: v for k, v in dev.items() if k.startswith(b.prefix)}, self.rt)
+        self.stream_parts = []
+        for prefix, part_spec in spec.stream_parts:
+            part = build_stream(part_spec)
+            part.bind({k[len(prefix):]: v for k, v in dev.items() if k.startswith(prefix)}, self.rt)
+            self.stream_parts.append(part)
+        for e, entry in enumerate(spec.schedule):
+            if entry.before is not None and not (0 <= entry.before[0] < len(self.stream_parts)):
+                raise invalid(f"schedule entry {e}: stream part {entry.before[0]} does not exist")
+        self.keep_embedding_output = any(getattr(p, "needs_embedding_output", False) for p in self.stream_parts)
         self.final_norm = build_norm(spec.final_norm)
         self.final_norm.bind({k[len("final_norm."):]: v for k, v in dev.items() if k.startswith("final_norm.")}, self.rt)
         self.embedding = dev["embedding.weight"]
         self.lm_head = self.embedding if spec.tie_embedding else dev["lm_head.weight"]
         self.cache_plan = CachePlan(spec, self.blocks)
         self.graph_safe = all(getattr(part, "graph_safe", True) for blk in self.blocks
-                              for _, part in getattr(blk, "parts", lambda: [])())
+                              for _, part in getattr(blk, "parts", lambda: [])()) and \
+            all(getattr(part, "graph_safe", True) for part in self.stream_parts)
         self.param_bytes = sum(t.numel() * t.element_size() for t in dev.values())
 
     @property
@@ -172,8 +191,12 @@ class Model:
         """Run the step's tokens; ``views[e]`` is the cache view of schedule entry e."""
         h = ops.embed_gather(ctx.token_ids, self.embedding, self.spec.embedding_scale)
         ctx.shared = {}
+        if self.keep_embedding_output:       # the stream is updated in place: a part that reads it later gets a copy
+            ctx.shared["embedding_output"] = h.clone()
         pending = (None, None)
         for e, entry in enumerate(self.spec.schedule):
+            if entry.before is not None:
+                h, pending = self.stream_parts[entry.before[0]].forward(h, pending, ctx, entry.before[1])
             pending = self.blocks[entry.layer].forward(h, pending, ctx, views[e])
         if ctx.n_rows == 0:
             # the last sublayer's output is only needed by the head; nothing to return

@@ -131,18 +131,46 @@ class DytParams:
         self.alpha, self.weight, self.bias = float(alpha), weight, bias
 
 
+class GroupRmsParams:
+    """One RMS norm in groups: a row is cut into ``groups`` equal consecutive parts, each divided by its own
+    ``sqrt(mean(part^2) + eps)``, and the whole row multiplied by ``weight``."""
+
+    __slots__ = ("weight", "eps", "groups")
+
+    def __init__(self, weight: torch.Tensor, eps: float, groups: int):
+        self.weight, self.eps, self.groups = weight, float(eps), int(groups)
+
+
 class PostNormed:
     """A sublayer's output that is normed before it is added to the residual stream: ``h += post(delta)``.
-    A norm that understands it does that add in the same pass as its own norm (``add_dyt``); any other
-    consumer calls :meth:`add_into` first and goes on with nothing pending."""
+    A norm that understands it does that add in the same pass as its own norm (``add_dyt`` for a Dynamic Tanh
+    ``post``, ``add_group_rmsnorm`` for an RMS norm in groups); any other consumer calls :meth:`add_into` first and
+    goes on with nothing pending."""
 
     __slots__ = ("delta", "post", "bias")
 
-    def __init__(self, delta: torch.Tensor, post: DytParams, bias: Optional[torch.Tensor] = None):
+    def __init__(self, delta: torch.Tensor, post, bias: Optional[torch.Tensor] = None):
         self.delta, self.post, self.bias = delta, post, bias      # bias: a vector added to delta before the norm
 
     def add_into(self, h: torch.Tensor) -> None:
-        add_dyt(h, self.delta, self.bias, self.post, None, None)
+        if isinstance(self.post, GroupRmsParams):
+            add_group_rmsnorm(h, self.delta, self.bias, self.post, None, None)
+        else:
+            add_dyt(h, self.delta, self.bias, self.post, None, None)
+
+
+def flush_pending(h: torch.Tensor, pending) -> None:
+    """Add what a sublayer left pending, ``(delta, bias)``, into the float32 stream now."""
+    delta, bias = pending
+    if delta is None:
+        return
+    if isinstance(delta, PostNormed):
+        delta.add_into(h)
+    elif isinstance(delta, SummedDeltas):
+        add_group_rmsnorm(h, delta.first, bias, None, None, None)
+        add_group_rmsnorm(h, delta.second, None, None, None, None)
+    else:
+        add_group_rmsnorm(h, delta, bias, None, None, None)
 
 
 class SummedDeltas:
@@ -188,19 +216,82 @@ def add_dyt(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional
     return out
 
 
+_lib.declare("gesso_add_group_rmsnorm", [_lib.P, _lib.P, _lib.I, _lib.P, _lib.P, _lib.P, _lib.F, _lib.I, _lib.P, _lib.I,
+                                          _lib.P, _lib.I, _lib.I, _lib.P])
+
+
+def add_group_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor],
+                      post: Optional[GroupRmsParams], pre: Optional[GroupRmsParams], out_dtype: Optional[torch.dtype],
+                      rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``h += post(delta (+ bias))`` in place (float32; ``post`` None: a plain add), returns ``pre(h)`` in ``out_dtype``
+    (``pre`` None: nothing), both RMS norms in groups, in one pass.  With ``rows`` only those rows are computed and
+    ``h`` stays.  ``post`` and ``pre`` share eps and the number of groups when both are given."""
+    _cuda_contig(h, "h", torch.float32)
+    N, H = h.shape
+    ref = pre or post
+    if post is not None and pre is not None:
+        _need(post.eps == pre.eps and post.groups == pre.groups, "the two norms of one pass share eps and groups")
+    for p in (post, pre):
+        if p is not None:
+            _cuda_contig(p.weight, "norm weight", torch.float32)
+            _need(p.weight.numel() == H and H % p.groups == 0, "norm weight or groups do not fit the row width")
+    if delta is not None:
+        _cuda_contig(delta, "delta")
+        _need(tuple(delta.shape) == (N, H), "delta shape differs from h")
+    if delta_bias is not None:
+        _cuda_contig(delta_bias, "delta_bias", torch.float32)
+        _need(delta is not None and delta_bias.numel() == H, "delta_bias needs a delta of the same width")
+    if rows is not None:
+        _cuda_contig(rows, "rows", torch.int32)
+    n_out = N if rows is None else rows.numel()
+    out = torch.empty((n_out, H), dtype=out_dtype, device=h.device) if pre is not None else None
+    _lib.check(_lib.library().gesso_add_group_rmsnorm(
+        _p(h), _p(delta), _dt(delta) if delta is not None else F32, _p(delta_bias),
+        _p(post.weight) if post else None, _p(pre.weight) if pre else None, ref.eps if ref else 0.0,
+        ref.groups if ref else 1, _p(out), _dt(out) if out is not None else F32, _p(rows), n_out, H, _stream()),
+        "add_group_rmsnorm")
+    return out
+
+
+_lib.declare("gesso_concat_cast", [_lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.P])
+_lib.declare("gesso_rows_add_vector", [_lib.P, _lib.P, _lib.I, _lib.I, _lib.P])
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``[a, b]`` side by side, two float32 ``[N, H]`` streams rounded to ``out_dtype``: the operand of a product that
+    mixes them."""
+    _cuda_contig(a, "a", torch.float32)
+    _cuda_contig(b, "b", torch.float32)
+    _need(a.dim() == 2 and a.shape == b.shape, "two streams of one shape")
+    N, H = a.shape
+    out = torch.empty((N, 2 * H), dtype=out_dtype, device=a.device)
+    _lib.check(_lib.library().gesso_concat_cast(_p(a), _p(b), _p(out), _dt(out), N, H, _stream()), "concat_cast")
+    return out
+
+
+def rows_add_vector(h: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """``h[r] += v`` for every row, in place (float32)."""
+    _cuda_contig(h, "h", torch.float32)
+    _cuda_contig(v, "v", torch.float32)
+    _need(h.dim() == 2 and v.numel() == h.shape[1], "one value per column")
+    _lib.check(_lib.library().gesso_rows_add_vector(_p(h), _p(v), h.shape[0], h.shape[1], _stream()), "rows_add_vector")
+    return h
+
+
 # ---- routed feed-forward ---------------------------------------------------------------------
-MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+MOE_SCORES = {"sigmoid": 0, "softmax": 1, "softmax_chosen": 2}
 MOE_ACTS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "glu_clamped": 3}
 MOE_GATED_ACTS = ("glu_clamped",)      # these take an expert's gate and up rows together: W_up [E, 2F, K]
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int,
               keep_groups: int, group_top: int = 2, score: str = "sigmoid", renorm: bool = False,
-              weight_scale: float = 1.0):
+              weight_scale: float = 1.0, logit_bias: Optional[torch.Tensor] = None):
     """Router of a mixture of experts: returns ``(expert ids int32 [N, top], weights float32 [N, top])`` in the
     order of the choice (best first).  The logits are a matrix product with float32 accumulation and a float32
     result (:func:`linear`: products of bfloat16 numbers are exact there, a float32 operand takes the FP32 FMA
-    kernel); scores, correction, groups, choice and weights are one float32 kernel."""
+    kernel); the logits' bias, scores, correction, groups, choice and weights are one float32 kernel.  ``score``
+    ``softmax_chosen``: experts are chosen by their logits and weighted by the softmax over the chosen logits only."""
     N = x.shape[0]
     E = w_router.shape[0]
     logits = linear(x, w_router, out_dtype=torch.float32)
@@ -208,10 +299,13 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     if correction is not None:
         _cuda_contig(correction, "correction", torch.float32)
         _need(correction.numel() == E, "one correction per expert")
+    if logit_bias is not None:
+        _cuda_contig(logit_bias, "router bias", torch.float32)
+        _need(logit_bias.numel() == E, "one router bias per expert")
     idx = torch.empty((N, top), dtype=torch.int32, device=x.device)
     w = torch.empty((N, top), dtype=torch.float32, device=x.device)
     _lib.check(_lib.library().gesso_moe_route(
-        _p(logits), _p(correction), _p(idx), _p(w), N, E, int(top), int(n_groups), int(keep_groups),
+        _p(logits), _p(logit_bias), _p(correction), _p(idx), _p(w), N, E, int(top), int(n_groups), int(keep_groups),
         int(group_top), MOE_SCORES[score], 1 if renorm else 0, float(weight_scale), _stream()), "moe_route")
     return idx, w
 
@@ -487,6 +581,53 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     return out
 
 
+_lib.declare("gesso_sigmoid_attention_generic",
+             [_lib.P, _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I,
+              _lib.I, _lib.F, _lib.P, _lib.I, _lib.F, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.P])
+
+
+def _check_head_gate(gate: Optional[torch.Tensor], n: int, nh: int, dtype) -> int:
+    """Row stride of a gate with one number per head, given as a view into a wider row-major tensor (0: no gate)."""
+    if gate is None:
+        return 0
+    _need(gate.is_cuda and gate.dim() == 2 and tuple(gate.shape) == (n, nh) and gate.stride(1) == 1
+          and gate.dtype == dtype, "gate must be [tokens, heads] of the run dtype with unit column stride")
+    return int(gate.stride(0))
+
+
+def _check_dist_bias(dist_bias: Optional[torch.Tensor], nh: int) -> int:
+    if dist_bias is None:
+        return 0
+    _cuda_contig(dist_bias, "distance bias", torch.float32)
+    _need(dist_bias.dim() == 2 and dist_bias.shape[0] == nh and dist_bias.shape[1] >= 1,
+          "the distance bias is a table [heads, distances]")
+    return int(dist_bias.shape[1])
+
+
+def sigmoid_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                              positions: torch.Tensor, seg_of_token: torch.Tensor, scale: float,
+                              dist_bias: Optional[torch.Tensor] = None, temp_coef: float = 0.0, temp_every: int = 0,
+                              gate: Optional[torch.Tensor] = None, window: Optional[int] = None) -> torch.Tensor:
+    """FP32-arithmetic attention with sigmoid weights over the pages: the key at distance n from the query of head
+    h has the weight ``sigmoid(q.k * scale * temp + dist_bias[h, min(n, last)])``, nothing is normalized over the keys;
+    ``temp = 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1)`` (1 with ``temp_every`` 0).  ``gate``: a 2-D
+    view ``[N, nh]`` with unit column stride whose sigmoid multiplies head h's result.  ``q`` may be float32 over
+    bfloat16 pages; the result ``[N, nh * value size]`` has the type of ``q``."""
+    _cuda_contig(q, "q")
+    N, nh, hd = q.shape
+    nkv, page_size, vd = k_pages.shape[1], k_pages.shape[2], v_pages.shape[2]
+    _need(k_pages.dtype == q.dtype or (q.dtype == torch.float32 and k_pages.dtype == torch.bfloat16),
+          "cache pages must have the dtype of q (or be bfloat16 under a float32 q)")
+    n_dist = _check_dist_bias(dist_bias, nh)
+    out = torch.empty((N, nh * vd), dtype=q.dtype, device=q.device)
+    gate_stride = _check_head_gate(gate, N, nh, k_pages.dtype)
+    _lib.check(_lib.library().gesso_sigmoid_attention_generic(
+        _p(q), _p(k_pages), _p(v_pages), _dt(k_pages), _p(block_table), block_table.shape[1], page_size, _p(positions),
+        _p(seg_of_token), _p(out), N, nh, nkv, hd, vd, float(scale), _p(dist_bias), n_dist, float(temp_coef),
+        int(temp_every), _p(gate), gate_stride, _dt(q), int(window or 0), _stream()), "sigmoid_attention_generic")
+    return out
+
+
 def _check_slopes(slopes: Optional[torch.Tensor], nh: int) -> None:
     if slopes is not None:
         _cuda_contig(slopes, "slopes", torch.float32)
@@ -686,7 +827,76 @@ def gated_rmsnorm(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch
     return out
 
 
+_lib.declare("gesso_gla", [_lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.F, _lib.F, _lib.P, _lib.LL, _lib.P, _lib.P, _lib.P,
+                            _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P])
+_lib.declare("gesso_head_gated_rmsnorm", [_lib.P, _lib.P, _lib.F, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I,
+                                           _lib.I, _lib.P])
+
+
+def gated_linear_attention(proj: torch.Tensor, z: torch.Tensor, z_bias: Optional[torch.Tensor], tau: float,
+                           q_scale: float, state: torch.Tensor, seg_start: torch.Tensor, slots: torch.Tensor,
+                           n_segs: int, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Linear attention with a decay per key channel and token, as a recurrence: ``a = sigmoid(z + z_bias) ** (1 /
+    tau)``, ``S = diag(a) S + k v^T``, ``o = S^T (q_scale * q)`` with q, k, v the columns of ``proj`` [N, >= 2*H*D +
+    H*Dv] (q, then k, then v, head by head) and ``z`` [N, H*D] float32.  ``state``: [slots, H, Dv, D] float32, read at
+    a segment's start and left as its last token makes it.  Returns o [N, H * Dv] float32."""
+    _need(proj.is_cuda and proj.dim() == 2 and proj.stride(1) == 1, "proj must be rows on the device")
+    H, D, Dv = int(n_heads), int(dim), int(vdim)
+    N = proj.shape[0]
+    _need(proj.shape[1] >= 2 * H * D + H * Dv, "proj is narrower than q, k and v")
+    _cuda_contig(z, "decay logits", torch.float32)
+    _need(tuple(z.shape) == (N, H * D), "one decay logit per token and key channel")
+    if z_bias is not None:
+        _cuda_contig(z_bias, "decay bias", torch.float32)
+        _need(z_bias.numel() == H * D, "one decay bias per key channel")
+    _need(state.dtype == torch.float32 and state.is_cuda and tuple(state.shape[1:]) == (H, Dv, D)
+          and state[0].is_contiguous(), "state must be [slots, heads, value size, key size] float32")
+    _cuda_contig(seg_start, "seg_start", torch.int32)
+    _cuda_contig(slots, "slots", torch.int32)
+    out = torch.empty((N, H * Dv), dtype=torch.float32, device=proj.device)
+    _lib.check(_lib.library().gesso_gla(_p(proj), _dt(proj), int(proj.stride(0)), _p(z), _p(z_bias), float(tau),
+                                        float(q_scale), _p(state), state.stride(0), _p(seg_start), _p(slots), _p(out), N,
+                                        int(n_segs), H, D, Dv, _stream()), "gated_linear_attention")
+    return out
+
+
+GATE_ACTS = {"sigmoid": 0, "silu": 1}
+
+
+def head_gated_rmsnorm(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, n_heads: int,
+                       out_dtype: torch.dtype, gate_act: str = "sigmoid") -> torch.Tensor:
+    """Per head of a row: ``o / sqrt(mean_head(o^2) + eps) * weight * act(gate)`` with float32 ``o`` [N, heads * Dv], a
+    ``weight`` [Dv] that all heads share, and ``gate`` a 2-D view [N, heads * Dv] of ``out_dtype`` with unit column
+    stride; ``act`` is ``sigmoid`` or ``silu``."""
+    _cuda_contig(o, "o", torch.float32)
+    _cuda_contig(weight, "weight", torch.float32)
+    N, W = o.shape
+    Dv = W // int(n_heads)
+    _need(Dv * n_heads == W and weight.numel() == Dv, "one norm weight per feature of a head")
+    _need(gate.is_cuda and tuple(gate.shape) == (N, W) and gate.stride(1) == 1 and gate.dtype == out_dtype,
+          "gate must be [rows, columns] of the output type with unit column stride")
+    out = torch.empty((N, W), dtype=out_dtype, device=o.device)
+    _lib.check(_lib.library().gesso_head_gated_rmsnorm(_p(o), _p(weight), float(eps), _p(gate), int(gate.stride(0)),
+                                                       _p(out), _dt(out), N, int(n_heads), Dv, GATE_ACTS[gate_act],
+                                                       _stream()), "head_gated_rmsnorm")
+    return out
+
+
 # ---- feed-forward ------------------------------------------------------------------------------
+_lib.declare("gesso_xielu", [_lib.P, _lib.P, _lib.I, _lib.LL, _lib.P, _lib.P])
+
+
+def xielu(x: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
+    """xIELU with the two learned numbers ``pq`` = (p, q) (float32, on the device): ``z > 0: softplus(p) z^2 + z / 2``,
+    ``z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2``; evaluated in float32."""
+    _cuda_contig(x, "x")
+    _cuda_contig(pq, "pq", torch.float32)
+    _need(pq.numel() == 2, "xielu takes two numbers")
+    out = torch.empty_like(x)
+    _lib.check(_lib.library().gesso_xielu(_p(x), _p(out), _dt(x), x.numel(), _p(pq), _stream()), "xielu")
+    return out
+
+
 def gelu_erf(x: torch.Tensor) -> torch.Tensor:
     """The exact gelu, ``0.5 x (1 + erf(x / sqrt 2))``, evaluated in float32."""
     _cuda_contig(x, "x")

@@ -18,6 +18,8 @@ Interfaces
                  ``forward(x, ctx, cache) -> (delta, delta_bias)``.
 ``FeedForward``  ``param_decls()``, ``bind(tensors, rt)``,
                  ``forward(x, ctx) -> (delta, delta_bias)``.
+``StreamPart``   acts on the residual stream between two layers:
+                 ``forward(h, pending, ctx, arg) -> (h, pending)``.
 ``Block``        the arrangement: owns the residual order of its parts,
                  ``forward(h, pending, ctx, cache) -> pending``.
 """
@@ -42,6 +44,8 @@ class ParamDecl:
     alt_shapes: Tuple[Tuple[int, ...], ...] = ()   # accepted spellings with unit axes
     init: str = "normal"                            # random-weights mode: normal | ones | zeros
     fan_in: Optional[int] = None
+    # axes whose size the checkpoint's tensor decides (``shape`` holds the size random weights are drawn with)
+    free_axes: Tuple[int, ...] = ()
 
 
 # ---- what a mixer needs from the cache manager -----------------------------------------
@@ -120,3 +124,16 @@ class Norm(Part):
 
 class Position(Part):
     pass
+
+
+class StreamPart(Part):
+    """Something that happens to the residual stream between two layers (a schedule entry names it in its
+    ``before``).  ``forward`` gets the float32 stream ``h``, what the last sublayer left pending, the step context and
+    the entry's argument; it returns the stream to go on with (``h`` itself or a new tensor) and what is still
+    pending.  ``needs_embedding_output``: the model keeps a copy of the embedding's output of the step in
+    ``ctx.shared["embedding_output"]`` for it."""
+
+    needs_embedding_output = False
+
+    def forward(self, h, pending, ctx, arg):
+        raise NotImplementedError

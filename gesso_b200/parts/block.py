@@ -87,8 +87,9 @@ class SandwichBlock:
         h = h + PostNorm_f( FeedForward(Norm_f(h)) )        (left out when the layer has no feed-forward)
 
     A sublayer's output travels on as ``pending = (PostNormed(delta, post norm), None)``: the next pre norm
-    norms it, adds it into the float32 stream and norms the sum in one kernel.  The post norms must be
-    Dynamic Tanh norms (the fused kernel's form); the pre norms may be any registered norm."""
+    norms it, adds it into the float32 stream and norms the sum in one kernel.  The post norms must be of a kind
+    that offers ``params()`` (Dynamic Tanh, RMS norm in groups: the fused kernels' forms); the pre norms may be any
+    registered norm."""
 
     def __init__(self, block_spec):
         self.spec = block_spec
@@ -106,7 +107,8 @@ class SandwichBlock:
             self.ff_post_norm = build_norm(block_spec.ff_post_norm)
         for n in (self.mixer_post_norm, self.ff_post_norm):
             if n is not None and not hasattr(n, "params"):
-                raise invalid("sandwich block: post norms must be of a kind that fuses with the residual add (dyt)")
+                raise invalid("sandwich block: post norms must be of a kind that fuses with the residual add "
+                              "(dyt, group_rmsnorm)")
 
     def parts(self):
         out = [("mixer_norm.", self.mixer_norm), ("mixer.", self.mixer), ("mixer_post_norm.", self.mixer_post_norm)]

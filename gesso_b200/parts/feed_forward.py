@@ -7,7 +7,9 @@
 into one matrix at bind time.
 
 ``mlp``: ``down( act(up(x)) )`` with one activation between two matrices, no biases; ``activation`` is a parameter
-(``gelu_erf``: the exact gelu, ``0.5 z (1 + erf(z / sqrt 2))``).  Its output is float32.
+(``gelu_erf``: the exact gelu, ``0.5 z (1 + erf(z / sqrt 2))``; ``xielu``: ``softplus(p) z^2 + z/2`` for ``z > 0`` and
+``(1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` otherwise, with the two learned numbers of the tensor ``act`` [2]).  Its
+output is float32.
 
 ``glu_clamped``: a gated unit with clamped inputs, ``down( g * sigmoid(1.702 g) * (u + 1) )`` with ``g = min(gate(x),
 limit)`` and ``u = clamp(up(x), -limit, limit)``; ``limit`` is a parameter.  Its output is float32.  (The routed
@@ -65,7 +67,8 @@ class SwiGLU(FeedForward):
 
 
 class MLP(FeedForward):
-    ACTIVATIONS = {"gelu_erf": ops.gelu_erf}
+    ACTIVATIONS = {"gelu_erf": ops.gelu_erf, "xielu": ops.xielu}
+    LEARNED = {"xielu": 2}          # activations with learned numbers: how many the tensor ``act`` holds
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -76,14 +79,19 @@ class MLP(FeedForward):
             raise invalid(f"mlp: unknown activation {self.act!r}; known: {sorted(self.ACTIVATIONS)}")
 
     def param_decls(self) -> Dict[str, ParamDecl]:
-        return {"up.weight": ParamDecl((self.ff, self.hidden), fan_in=self.hidden),
-                "down.weight": ParamDecl((self.hidden, self.ff), fan_in=self.ff)}
+        d = {"up.weight": ParamDecl((self.ff, self.hidden), fan_in=self.hidden),
+             "down.weight": ParamDecl((self.hidden, self.ff), fan_in=self.ff)}
+        if self.act in self.LEARNED:
+            d["act"] = ParamDecl((self.LEARNED[self.act],), role="vector", init="zeros")
+        return d
 
     def bind(self, tensors, rt) -> None:
         self.w_up, self.w_down = tensors["up.weight"], tensors["down.weight"]
+        self.act_params = tensors.get("act")
 
     def forward(self, x, ctx):
-        a = self.ACTIVATIONS[self.act](ops.linear(x, self.w_up, out_dtype=x.dtype))
+        u = ops.linear(x, self.w_up, out_dtype=x.dtype)
+        a = self.ACTIVATIONS[self.act](u, self.act_params) if self.act in self.LEARNED else self.ACTIVATIONS[self.act](u)
         return ops.linear(a, self.w_down, out_dtype=torch.float32), None
 
 

@@ -1,4 +1,4 @@
-"""RMSNorm with the residual add folded in.
+"""Norms with the residual add folded in: RMSNorm, Dynamic Tanh, RMS norm in groups.
 
 ``y = (x / sqrt(mean(x^2) + eps)) * w`` over the last axis, divide first, scale
 second (src/Operators/cpu.jl:293-311).  The residual stream is float32; the sum
@@ -19,6 +19,7 @@ from typing import Dict
 import torch
 
 from .. import ops
+from ..errors import invalid
 from .base import Norm, ParamDecl
 from .registry import register_norm
 
@@ -106,5 +107,56 @@ class DynamicTanh(Norm):
         return ops.add_dyt(h, delta, delta_bias, post, self.p, self.out_dtype, rows)
 
 
+class GroupRMSNorm(Norm):
+    """RMS norm in groups: a row is cut into ``groups`` equal consecutive parts; each part is divided by its own
+    ``sqrt(mean(part^2) + eps)``, then the whole row is multiplied by ``weight``.  Parameters: ``size``, ``eps``,
+    ``groups`` (default 1: the ordinary RMS norm).  Tensor: ``weight`` [size].
+
+    ``add_norm`` adds the pending delta into the float32 stream and norms the sum in one kernel; a pending
+    :class:`~gesso_b200.ops.PostNormed` whose own norm is of this kind (with the same eps and groups) is normed and
+    added in the same pass.  ``params()`` hands the norm to such a caller.  Statistics, sums and the scaling are
+    float32; only the result is rounded to the run type."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.groups = int(spec.get("groups") or 1)
+        if self.groups < 1 or self.size % self.groups != 0:
+            raise invalid(f"group_rmsnorm: {self.size} features do not form {self.groups} equal groups")
+        self.p = None
+        self.out_dtype = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {"weight": ParamDecl((self.size,), role="vector", init="ones")}
+
+    def bind(self, tensors, rt) -> None:
+        self.p = ops.GroupRmsParams(tensors["weight"], self.eps, self.groups)
+        self.out_dtype = rt.dtype
+
+    def params(self) -> "ops.GroupRmsParams":
+        return self.p
+
+    def add_norm(self, h, delta, delta_bias, rows=None):
+        post = None
+        if isinstance(delta, ops.PostNormed):
+            fits = isinstance(delta.post, ops.GroupRmsParams) and \
+                (delta.post.eps, delta.post.groups) == (self.eps, self.groups)
+            if fits:
+                delta, post, delta_bias = delta.delta, delta.post, delta.bias
+            elif rows is None:
+                delta.add_into(h)
+                delta = None
+            else:
+                raise NotImplementedError("group_rmsnorm: a delta with another kind of post norm cannot be added for a row list")
+        elif isinstance(delta, ops.SummedDeltas):
+            if rows is not None:
+                raise NotImplementedError("group_rmsnorm: two summed deltas cannot be added for a row list")
+            ops.flush_pending(h, (delta, delta_bias))
+            delta = delta_bias = None
+        return ops.add_group_rmsnorm(h, delta, delta_bias, post, self.p, self.out_dtype, rows)
+
+
+register_norm("group_rmsnorm", GroupRMSNorm, replace=True)
 register_norm("rmsnorm", RMSNorm, replace=True)
 register_norm("dyt", DynamicTanh, replace=True)

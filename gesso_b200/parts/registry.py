@@ -12,7 +12,7 @@ from ..config.spec import PartSpec
 from ..errors import invalid
 
 _TABLES: Dict[str, Dict[str, Callable]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "stream": {},
 }
 
 
@@ -45,6 +45,10 @@ def register_position(kind: str, cls: Callable, *, replace: bool = False) -> Non
     _register("position", kind, cls, replace)
 
 
+def register_stream(kind: str, cls: Callable, *, replace: bool = False) -> None:
+    _register("stream", kind, cls, replace)
+
+
 def register_block(arrangement: str, cls: Callable, *, replace: bool = False) -> None:
     _register("block", arrangement, cls, replace)
 
@@ -67,6 +71,10 @@ def build_norm(spec: PartSpec):
 
 def build_position(spec: PartSpec):
     return _build("position", spec)
+
+
+def build_stream(spec: PartSpec):
+    return _build("stream", spec)
 
 
 def build_block(block_spec):

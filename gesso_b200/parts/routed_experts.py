@@ -3,7 +3,9 @@
 Expert e computes ``W_down[e] act(W_up[e] x)`` (no biases; ``act`` is ``relu2`` = the square of relu,
 ``silu`` or ``gelu_tanh``).  The router scores every expert for every token in float32::
 
-    z = W_router x,   s = sigmoid(z)   (or softmax over the experts)
+    z = W_router x (+ b_router),   s = sigmoid(z)   (or softmax over the experts, or ``softmax_chosen``: experts are
+                                                     chosen by z itself and weighted by the softmax over the chosen
+                                                     logits only)
     c = s + correction                 (the score an expert is CHOSEN by; ``correction`` is optional)
 
 Experts form ``n_groups`` equal groups of neighbours; a group's score is the sum of its ``group_top``
@@ -21,7 +23,7 @@ token; the routed sum is added to its output.
 
 Parameters (all from the part spec): hidden_size, ff_dim, n_experts, top_k, n_groups (1), keep_groups
 (= n_groups), group_top (2), score ("sigmoid"), correction (false), renormalize (false), weight_scale
-(1.0), activation ("relu2").  Tensors: ``router.weight`` [E, hidden] (the logits are a product with float32
+(1.0), activation ("relu2"), router_bias (false; tensor ``router.bias`` [E]).  Tensors: ``router.weight`` [E, hidden] (the logits are a product with float32
 accumulation and a float32 result, everything after them is float32 whatever the run type), ``correction``
 [E], ``experts.<e>.up.weight`` [ff, hidden],
 ``experts.<e>.down.weight`` [hidden, ff]; the experts' matrices are stacked at bind time.
@@ -54,6 +56,7 @@ class RoutedExperts(FeedForward):
         self.group_top = int(spec.get("group_top") or 2)
         self.score = str(spec.get("score", "sigmoid"))
         self.has_correction = bool(spec.get("correction", False))
+        self.has_router_bias = bool(spec.get("router_bias", False))
         self.renorm = bool(spec.get("renormalize", False))
         self.weight_scale = float(spec.get("weight_scale", 1.0))
         self.act = str(spec.get("activation", "relu2"))
@@ -82,6 +85,8 @@ class RoutedExperts(FeedForward):
         d = {"router.weight": ParamDecl((self.E, self.hidden), fan_in=self.hidden)}
         if self.has_correction:
             d["correction"] = ParamDecl((self.E,), role="vector", init="zeros")
+        if self.has_router_bias:
+            d["router.bias"] = ParamDecl((self.E,), role="vector", init="zeros")
         for e in range(self.E):
             if self.gated:
                 d[f"experts.{e}.gate.weight"] = ParamDecl((self.ff, self.hidden), fan_in=self.hidden)
@@ -95,6 +100,7 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors, rt) -> None:
         self.w_router = tensors["router.weight"]
         self.correction = tensors.get("correction")
+        self.router_bias = tensors.get("router.bias")
         ups = [tensors[f"experts.{e}.up.weight"] for e in range(self.E)]
         downs = [tensors[f"experts.{e}.down.weight"] for e in range(self.E)]
         gates = [tensors[f"experts.{e}.gate.weight"] for e in range(self.E)] if self.gated else []
@@ -117,7 +123,7 @@ class RoutedExperts(FeedForward):
             if bias is not None or base.dtype != torch.float32:
                 raise invalid("routed experts: the shared expert must give a float32 output without a bias")
         idx, w = ops.moe_route(x, self.w_router, self.correction, self.top, self.n_groups, self.keep_groups,
-                               self.group_top, self.score, self.renorm, self.weight_scale)
+                               self.group_top, self.score, self.renorm, self.weight_scale, self.router_bias)
         if ops.moe_grouped_takes(x, self.w_up, self.w_down, self.top, self.act, self.packed):
             return ops.moe_experts_grouped(x, self.w_up, self.w_down, idx, w, self.act, self.limit, add_to=base), None
         return ops.moe_experts_pairs(x, self.w_up, self.w_down, idx, w, self.act, self.limit, self.packed,

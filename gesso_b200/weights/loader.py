@@ -19,7 +19,7 @@ import torch
 from ..config.spec import ModelSpec
 from ..errors import invalid
 from ..parts.base import ParamDecl
-from ..parts.registry import build_block, build_norm
+from ..parts.registry import build_block, build_norm, build_stream
 
 
 def model_param_decls(spec: ModelSpec) -> Dict[str, ParamDecl]:
@@ -31,6 +31,9 @@ def model_param_decls(spec: ModelSpec) -> Dict[str, ParamDecl]:
         blk = build_block(b)
         for name, d in blk.param_decls().items():
             decls[b.prefix + name] = d
+    for prefix, part_spec in spec.stream_parts:
+        for name, d in build_stream(part_spec).param_decls().items():
+            decls[prefix + name] = d
     for name, d in build_norm(spec.final_norm).param_decls().items():
         decls["final_norm." + name] = d
     if not spec.tie_embedding:
@@ -53,6 +56,13 @@ def bind_tensors(spec: ModelSpec, found: Dict[str, torch.Tensor]) -> Dict[str, t
         used.add(hit)
         t = found[hit]
         shape = tuple(t.shape)
+        if decl.free_axes:
+            want = tuple("any" if a in decl.free_axes else d for a, d in enumerate(decl.shape))
+            if len(shape) != len(want) or any(w != "any" and w != d for w, d in zip(want, shape)) or 0 in shape:
+                misshaped.append(f"{hit}: expected {want}, found {shape}")
+                continue
+            out[internal] = t
+            continue
         if shape != tuple(decl.shape) and shape not in decl.alt_shapes:
             misshaped.append(f"{hit}: expected {tuple(decl.shape)}, found {shape}")
             continue
