@@ -224,3 +224,124 @@ class PlainMabidra:
             if taps is not None:
                 taps.append(x.clone())
         return self.norm(x, self.T["final.norm"]) @ self.T["head"].T
+
+    # ---- what the tests ask of a model ------------------------------------------------------------------------
+    @staticmethod
+    def from_dir(model_dir: str) -> "PlainMabidra":
+        import json
+        import os
+        from gesso_b200.weights.safetensors_io import read_safetensors_file
+        with open(os.path.join(model_dir, "config.json")) as f:
+            cfg = json.load(f)
+        return PlainMabidra(cfg, read_safetensors_file(os.path.join(model_dir, "model.safetensors")))
+
+    def logits(self, tokens) -> torch.Tensor:
+        return self.forward(list(tokens))
+
+    def stream(self, tokens) -> torch.Tensor:
+        taps: list = []
+        self.forward(list(tokens), taps=taps)
+        return torch.stack(taps)
+
+    def margins(self, tokens) -> torch.Tensor:
+        """Per position: the smallest gap, over the routed layer runs, between the last chosen logit and the best one
+        left out (infinite where every expert is chosen or no layer routes).  A bfloat16 run may choose otherwise
+        where this is small."""
+        tokens = list(tokens)
+        out = torch.full((len(tokens),), math.inf, dtype=F64)
+        x = self.T["embed"][torch.tensor(tokens, dtype=torch.long)] * float(self.cfg["embedding"]["scale"])
+        x0 = x
+        for run in layer_order(self.cfg):
+            if run["pass"] is not None:
+                x = torch.cat([x, x0], dim=1) @ self.T["loop.in"].T + self.T["loop.step"][run["pass"]]
+            i = run["layer"]
+            L, P = self.cfg["layers"][i], self.layer_tensors(i)
+            mlp = L.get("mlp")
+            if mlp is not None and mlp["kind"] == "moe" and mlp["router"]["top"] < mlp["router"]["experts"]:
+                n1 = self.norm(x, P["norm1"])
+                d = mixer_gla(n1, P, L["mixer"], self.eps) if L["type"] == "gla" else mixer_attention(n1, P, L["mixer"], self.eps)
+                mid = x + self.norm(d, P["norm1b"])
+                z = self.norm(mid, P["norm2"]) @ P["mlp.router"].T + P["mlp.router.b"]
+                top = torch.sort(z, dim=-1, descending=True).values
+                k = int(mlp["router"]["top"])
+                out = torch.minimum(out, top[:, k - 1] - top[:, k])
+            x = self.layer(x, i)
+        return out
+
+    def greedy(self, prompt, n_new: int):
+        ids = list(prompt)
+        for _ in range(n_new):
+            ids.append(int(self.logits(ids)[-1].argmax()))
+        return ids
+
+
+# ---- random models for the tests -----------------------------------------------------------------------
+def random_tensors(cfg: dict, seed: int, decay_rank: int = 5, bias_rows: int = 12) -> Dict[str, torch.Tensor]:
+    """Tensors under their checkpoint names, rounded to bfloat16 (every run type sees the same numbers), drawn so that
+    nothing is flat: projections N(0, gain^2 / fan_in), norm weights around one, biases and tables of order 0.3 to
+    1.5, the decay's bias so that decays spread between slow and fast, the re-entry matrix near [I, I] / 2."""
+    g = torch.Generator().manual_seed(seed)
+    W: Dict[str, torch.Tensor] = {}
+
+    def rnd(*shape, std=1.0, mean=0.0):
+        return (mean + torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+
+    def mat(rows, cols, gain=1.5):
+        return rnd(rows, cols, std=gain / math.sqrt(cols))
+
+    Wd, V = cfg["width"], cfg["vocab"]
+    W["embed"] = rnd(V, Wd)
+    W["head"] = mat(V, Wd, 1.0)
+    W["final.norm"] = rnd(Wd, std=0.2, mean=1.0)
+    if cfg.get("loop"):
+        eye = torch.cat([torch.eye(Wd), torch.eye(Wd)], dim=1) * 0.5
+        W["loop.in"] = (eye + torch.randn(Wd, 2 * Wd, generator=g) * 0.3 / math.sqrt(2 * Wd)).to(torch.bfloat16)
+        W["loop.step"] = rnd(int(cfg["loop"]["times"]), Wd, std=0.3)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if L.get("mlp") is not None else ()):
+            W[p + n] = rnd(Wd, std=0.2, mean=1.0)
+        H, D = m["heads"], m["dim"]
+        Dv = m.get("vdim", D)
+        if L["type"] == "gla":
+            W[p + "mix.q"], W[p + "mix.k"] = mat(H * D, Wd), mat(H * D, Wd)
+            W[p + "mix.v"], W[p + "mix.g"] = mat(H * Dv, Wd), mat(H * Dv, Wd)
+            W[p + "mix.a1"], W[p + "mix.a2"] = mat(decay_rank, Wd), mat(H * D, decay_rank, 2.0)
+            W[p + "mix.a2.b"] = rnd(H * D, std=2.0, mean=2.0)
+            W[p + "mix.norm"] = rnd(Dv, std=0.2, mean=1.0)
+            W[p + "mix.o"] = mat(Wd, H * Dv)
+        else:
+            G = m["kv_heads"]
+            for n, rows in (("q", H * D), ("k", G * D), ("v", G * Dv)):
+                W[p + "mix." + n] = mat(rows, Wd)
+                W[p + "mix." + n + ".b"] = rnd(rows, std=0.3)
+            W[p + "mix.q.norm"] = rnd(D, std=0.2, mean=1.0)
+            W[p + "mix.k.norm"] = rnd(D, std=0.2, mean=1.0)
+            W[p + "mix.rel"] = rnd(bias_rows, H, std=1.5)
+            W[p + "mix.pb"] = rnd(H, std=1.0, mean=-1.0)
+            W[p + "mix.g"] = mat(H, Wd, 2.0)
+            W[p + "mix.o"] = mat(Wd, H * Dv)
+            W[p + "mix.o.b"] = rnd(Wd, std=0.3)
+        mlp = L.get("mlp")
+        if mlp is None:
+            continue
+        if mlp["kind"] == "dense":
+            W[p + "mlp.up"], W[p + "mlp.down"] = mat(mlp["ff"], Wd), mat(Wd, mlp["ff"])
+            W[p + "mlp.act"] = rnd(2, std=1.0)
+        else:
+            F = mlp["expert"]["ff"]
+            W[p + "mlp.router"] = mat(mlp["router"]["experts"], Wd, 3.0)
+            W[p + "mlp.router.b"] = rnd(mlp["router"]["experts"], std=0.5)
+            for e in range(mlp["router"]["experts"]):
+                W[f"{p}mlp.e{e}.up"], W[f"{p}mlp.e{e}.down"] = mat(F, Wd), mat(Wd, F)
+    return W
+
+
+def write_model(model_dir: str, cfg: dict, seed: int, **sizes) -> None:
+    import json
+    import os
+    from gesso_b200.weights.safetensors_io import write_safetensors_file
+    os.makedirs(model_dir, exist_ok=True)
+    with open(os.path.join(model_dir, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors_file(os.path.join(model_dir, "model.safetensors"), random_tensors(cfg, seed, **sizes))
