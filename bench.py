@@ -49,6 +49,10 @@ a step;
                                              # feed-forwards in parallel with the mixer) at two sizes beside Sodurax
                                              # layers of equal size: prefill and decode throughput, kernels by name
 
+    python bench.py --workload mabidra       # Mabidra layers (gated linear attention, sigmoid attention with a distance
+                                             # bias, group norms around each sublayer, xIELU and squared-relu experts)
+                                             # beside Memipel lightning and attention layers of equal size
+
 a table (not JSON) of where a step's time goes, from the CUPTI activity trace.
 
 Peaks come from ``MEASURED_PEAKS.json`` beside this file when the driver wrote it, else the
@@ -730,6 +734,129 @@ def memipel_workload(args) -> int:
         "peaks": pk, "sizes": out, "clocks": sampler.summary()}))
     return 0
 
+# ---- Mabidra beside Memipel at equal size -----------------------------------------------------------------------
+# Six layers, gated linear attention and sigmoid attention in turn; the first layer's feed-forward is dense, the
+# others are routed.  The Memipel model beside it has lightning layers (a fixed decay per head instead of a computed
+# one per key channel) and softmax attention layers of the same width, heads and experts in the same order: its
+# closest relative (a recurrence over a per-request state beside paged attention, routed experts).
+MABIDRA_SIZES = {
+    "w1024": dict(width=1024, heads=16, kv=4, dim=64, gla_heads=16, gla_dim=64, rank=16, experts=16, ff=512, top=4, groups=4),
+    "w2048": dict(width=2048, heads=32, kv=8, dim=64, gla_heads=16, gla_dim=128, rank=16, experts=32, ff=1024, top=4, groups=8),
+    # values wider than keys in the recurrence, and heads of 128 features in the attention
+    "w2048v256": dict(width=2048, heads=16, kv=4, dim=128, gla_heads=8, gla_dim=128, gla_vdim=256, rank=32, experts=32,
+                      ff=1024, top=4, groups=8),
+}
+MABIDRA_LAYERS = 6
+
+
+def mabidra_configs(z):
+    H, D, Dv = z["gla_heads"], z["gla_dim"], z.get("gla_vdim", z["gla_dim"])
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    gla = {"type": "gla", "mixer": {"heads": H, "dim": D, "vdim": Dv, "tau": 16.0, "decay_rank": z["rank"]}, "mlp": moe}
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
+                                          "scale": z["dim"] ** -0.5, "bias_max": 4096.0,
+                                          "q_temp": {"coef": 0.1, "every": 512}}, "mlp": moe}
+    mbd = {"architecture": "Mabidra", "vocab": SODURAX_VOCAB, "width": z["width"], "embedding": {"scale": 1.0},
+           "norm": {"eps": 1e-6, "groups": 4}, "loop": None,
+           "layers": [dict(gla, mlp=dense), att, gla, att, gla, att]}
+    mmoe = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0},
+            "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["groups"]}}}
+    lightning = {"type": "lightning", "mixer": {"heads": H, "dim": D, "vdim": Dv,
+                                                "decay": [1.0 - 2.0 ** -(1 + 8 * h / H) for h in range(H)]}, "mlp": mmoe}
+    matt = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
+                                           "scale": z["dim"] ** -0.5, "conv": None, "v_mix": False, "mask": None}, "mlp": mmoe}
+    mmp = {"architecture": "Memipel", "vocab": SODURAX_VOCAB, "width": z["width"], "norm": {"eps": 1e-6},
+           "layers": [dict(lightning, mlp=dense), matt, lightning, matt, lightning, matt]}
+    return mbd, mmp
+
+
+def mabidra_workload(args) -> int:
+    import torch
+    import gesso_b200 as gb
+    from gesso_b200.engine.batch import StepEntry
+    from gesso_b200.engine.engine import Engine
+    from gesso_b200 import ops
+    pk = peaks()
+    warmup = max(args.warmup, 3)
+    steps = min(args.steps, 64)
+    sampler = ClockSampler(device_uuid())
+    sampler.start()
+    out = {}
+    for name, z in MABIDRA_SIZES.items():
+        if (args.sizes and name not in args.sizes.split(",")) or (not args.sizes and name == "w2048v256"):
+            continue
+        row = {}
+        for which, cfg in zip(("mabidra", "memipel"), mabidra_configs(z)):
+            model = gb.random_model(cfg, seed=0, dtype="bfloat16", max_positions=args.context, style="fan_in")
+            ms_pre = time_prefill(gb, model, args.prefill_tokens, args.page_size)
+            ms_dec, launches, kv_mid = time_decode(gb, model, args.batch, args.context, steps, warmup, args.page_size)
+            # Bytes of a decoding step: the matrices it reads once (routed experts: those that batch * top pairs touch)
+            # and what a query reads of the cache (every earlier key and value; a recurrent state is read and written).
+            # Flops of a prefill step: the matrices a token uses, the causal attention and the recurrence (the outer
+            # product into the state and the read-out).
+            W, H, G, D, T = z["width"], z["heads"], z["kv"], z["dim"], args.prefill_tokens
+            LH, LD, LV, R = z["gla_heads"], z["gla_dim"], z.get("gla_vdim", z["gla_dim"]), z["rank"]
+            touched = min(z["experts"], args.batch * z["top"])
+            n_ff = 3 if which == "memipel" else 2            # matrices of an expert
+            moe_dec = touched * n_ff * z["ff"] * W + z["experts"] * W
+            moe_tok = z["top"] * n_ff * z["ff"] * W + z["experts"] * W
+            dense = 2 * z["top"] * z["ff"] * W
+            if which == "mabidra":
+                rec_w = W * (2 * LH * LD + 2 * LH * LV + R) + R * LH * LD + LH * LV * W
+                att_w = W * (H * D + 2 * G * D + H) + H * D * W
+            else:
+                rec_w = W * (2 * LH * LD + 2 * LH * LV) + LH * LV * W
+                att_w = W * (H * D + 2 * G * D) + H * D * W
+            w_dec = 3 * (rec_w + att_w) + dense + 5 * moe_dec
+            w_tok = 3 * (rec_w + att_w) + dense + 5 * moe_tok
+            cache = 3 * (2 * LH * LD * LV * 4 + kv_mid * 2 * G * D * 2)
+            attn = 3 * (2 * LH * LD * LV + 2 * (T / 2) * H * D)
+            head = SODURAX_VOCAB * W
+            dec_bytes = 2 * (w_dec + head) + args.batch * cache
+            pre_flops = T * 2 * (w_tok + attn)
+            row[which] = {
+                "prefill_ms": round(ms_pre, 4), "prefill_tok_s": round(T * 1000 / ms_pre, 1),
+                "prefill_frac_of_bf16_peak": round(pre_flops / (ms_pre * 1e-3) / 1e12 / pk["bf16_tflops"], 4),
+                "decode_ms_per_step": round(ms_dec, 4), "decode_tok_s": round(args.batch * 1000 / ms_dec, 1),
+                "decode_frac_of_hbm_peak": round(dec_bytes / (ms_dec * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                "gpu_launches_per_decode_step": launches // steps}
+            if args.kernels:
+                eng = Engine(model, max_positions=args.context, page_size=args.page_size,
+                             num_pages=(args.batch + 1) * (args.context // args.page_size + 1), max_requests=args.batch + 1)
+                g = torch.Generator().manual_seed(5)
+                prompt = torch.randint(0, model.vocab_size, (T,), generator=g).tolist()
+                for i in range(args.batch):
+                    eng.admit(i)
+                    eng.step([StepEntry(i, prompt, [])])
+                n_pre = [0]
+
+                def pre():
+                    rid = f"p{n_pre[0]}"
+                    n_pre[0] += 1
+                    eng.admit(rid)
+                    eng.step([StepEntry(rid, prompt, [T - 1])])
+                    eng.release(rid)
+
+                def dec():
+                    ops.argmax_rows(eng.step([StepEntry(i, [7 + i], [0]) for i in range(args.batch)]))
+                for _ in range(3):                  # the steps' graphs are captured
+                    pre(), dec()
+                row[which]["prefill_kernels_us"] = kernels_by_name(pre)
+                row[which]["decode_kernels_us"] = kernels_by_name(dec)
+                eng.check_status()
+            del model
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = round(row["mabidra"]["prefill_tok_s"] / row["memipel"]["prefill_tok_s"], 3)
+        row["decode_ratio"] = round(row["mabidra"]["decode_tok_s"] / row["memipel"]["decode_tok_s"], 3)
+        out[name] = dict(row, sizes=z)
+    print(json.dumps({
+        "workload": "mabidra", "metric": "prefill and decode tokens/s of Mabidra layers beside Memipel layers of equal size",
+        "unit": "tokens/s", "layers": MABIDRA_LAYERS, "vocab": SODURAX_VOCAB, "batch": args.batch, "context": args.context,
+        "prefill_tokens": args.prefill_tokens, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random weights seed 0)",
+        "peaks": pk, "sizes": out, "clocks": sampler.summary()}))
+    return 0
+
 
 def reference_arm():
     """The reference is a Julia 1.12 project (Project.toml, no setup.py / pyproject.toml): pip cannot
@@ -753,12 +880,13 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "timeline", "sodurax", "memipel"] + sorted(SERVE),
+    ap.add_argument("--workload", default="decode", choices=["decode", "timeline", "sodurax", "memipel", "mabidra"] + sorted(SERVE),
                     help="decode: the headline (default); serve350m / serve700m: serving-like runs through run_batch; "
                          "timeline: the kernels of one decoding step at --batch and --context; sodurax: Sodurax layers "
-                         "beside LFM2 attention layers of equal size; memipel: Memipel layers beside Sodurax layers of equal size")
-    ap.add_argument("--sizes", default="", help="sodurax / memipel workload: which of its sizes to run, with commas (default: all)")
-    ap.add_argument("--kernels", action="store_true", help="sodurax / memipel workload: also the kernels of a step by name")
+                         "beside LFM2 attention layers of equal size; memipel: Memipel layers beside Sodurax layers of equal size; "
+                         "mabidra: Mabidra layers beside Memipel layers of equal size")
+    ap.add_argument("--sizes", default="", help="sodurax / memipel / mabidra workload: which of its sizes to run, with commas (default: all)")
+    ap.add_argument("--kernels", action="store_true", help="sodurax / memipel / mabidra workload: also the kernels of a step by name")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -771,6 +899,8 @@ def main() -> int:
         return sodurax_workload(args)
     if args.workload == "memipel":
         return memipel_workload(args)
+    if args.workload == "mabidra":
+        return mabidra_workload(args)
     if args.workload != "decode":
         return serve_workload(args.workload)
     warmup = max(args.warmup, 3)

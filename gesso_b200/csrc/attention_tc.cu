@@ -14,6 +14,9 @@
 //     one feature, contiguous because V pages are stored [feature][slot].  The 16 keys of a block
 //     are assigned to the two 8-key score tiles so that a thread's four probabilities are keys
 //     4t..4t+3, which is one 8-byte read of a V^T row.
+// SIGMOID kernels (attention whose weights are sigmoids of the scores, nothing normalized over the keys) share the
+// fragments and the walks: a weight is sigmoid(q.k * scale * temp(position) + bias[head][distance]), there is no
+// running maximum and no denominator, the pieces of a split add up as they are.
 // Softmax statistics and the output accumulate in float32 with a running maximum (base-2
 // exponentials with the 1/sqrt(d) scale folded in; the maximum is rounded up to a whole number, see
 // attend_block).  Reference design inputs: the split-K decode
@@ -84,6 +87,22 @@ __device__ __forceinline__ void load_block(KVFrag<HD>& f, const bf16* __restrict
     for (int j = 0; j < HD / 8; ++j) f.v[j] = *reinterpret_cast<const uint2*>(vt + (size_t)(8 * j) * page_size);
 }
 
+// What the sigmoid kernels take beside the softmax ones: a float32 table [heads][n_dist] added to the scores by
+// distance (every distance from n_dist - 1 on reads the last column; null: none), a temperature on the queries,
+// 1 + coef * ln(floor((position + 1) / every) + 1) (every <= 0: 1), and whether the output gate is one number per
+// head (element [token * gate_stride + head]) instead of one per feature.
+struct SigmoidArgs {
+    const float* bias;
+    int n_dist;
+    float temp_coef;
+    int temp_every;
+    int gate_per_head;
+};
+
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+    return every > 0 ? 1.f + coef * logf((float)((pos + 1) / every + 1)) : 1.f;
+}
+
 // One 16-key block against one m16 tile of queries: scores, running softmax, outputs.
 // qf[c] / qg[c]: Q rows g and g+8, features 32c+8t..+8.  pos_a / pos_b: last visible key of rows g
 // and g+8; lo_a / lo_b: first visible key.  key0: first key of the block.
@@ -93,12 +112,19 @@ __device__ __forceinline__ void load_block(KVFrag<HD>& f, const bf16* __restrict
 // as the sum of two bfloat16 numbers (its rounding and the rounding of what is left), i.e. with 16 bits of
 // mantissa instead of 8, for mixers whose attention weights are to act in 32-bit precision.
 // slope_a / slope_b: the distance bias of the heads in rows g and g+8 (0: none), times log2(e).
-template <int HD, bool UPPER = true, bool PSPLIT = false>
+// scale_a / scale_b: what the scores of rows g and g+8 are multiplied by (base-2 domain for the softmax).
+// SIGMOID: the weights are sigmoid(score * scale + bias[distance]) for the visible keys and 0 for the others;
+// m and l stay as they are (the callers start m at 0, so that merging pieces adds them up); bias_a / bias_b: the
+// rows' tables by distance (null: none); pos_max: the last position among all rows of the tile.
+template <int HD, bool UPPER = true, bool PSPLIT = false, bool SIGMOID = false>
 __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&qf)[HD / 32],
                                              const uint4 (&qg)[HD / 32], float (&o)[HD / 8][4], float (&m)[2],
                                              float (&l)[2], int key0, int t, int pos_a, int pos_b, int lo_a,
-                                             int lo_b, float scale_log2, bool need_mask, int keep = 0,
-                                             float slope_a = 0.f, float slope_b = 0.f) {
+                                             int lo_b, float scale_a, float scale_b, bool need_mask, int keep = 0,
+                                             float slope_a = 0.f, float slope_b = 0.f,
+                                             const float* __restrict__ bias_a = nullptr,
+                                             const float* __restrict__ bias_b = nullptr, int n_dist = 0,
+                                             int pos_max = 0) {
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
@@ -111,11 +137,26 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
     float sa[4] = {s0[0], s0[1], s1[0], s1[1]};
     float sb[4] = {s0[2], s0[3], s1[2], s1[3]};
     const int kbase = key0 + 4 * t;
+    float pa[4], pb[4] = {0.f, 0.f, 0.f, 0.f};
+    float alpha_a = 1.f, alpha_b = 1.f;
+    if (SIGMOID) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = kbase + i;
+            float xa = sa[i] * scale_a, xb = sb[i] * scale_b;
+            if (bias_a) xa += __ldg(bias_a + min(max(pos_a - key, 0), n_dist - 1));
+            if (UPPER && bias_b) xb += __ldg(bias_b + min(max(pos_b - key, 0), n_dist - 1));
+            const bool on_a = !need_mask || (key <= pos_a && (key >= lo_a || key < keep));
+            const bool on_b = UPPER && (!need_mask || (key <= pos_b && (key >= lo_b || key < keep)));
+            pa[i] = on_a ? 1.f / (1.f + __expf(-xa)) : 0.f;
+            pb[i] = on_b ? 1.f / (1.f + __expf(-xb)) : 0.f;
+        }
+    } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         // a distance bias: slope * (query position - key position) is taken off (slopes in the base-2 domain)
-        sa[i] = sa[i] * scale_log2 - slope_a * (float)(pos_a - (kbase + i));
-        if (UPPER) sb[i] = sb[i] * scale_log2 - slope_b * (float)(pos_b - (kbase + i));
+        sa[i] = sa[i] * scale_a - slope_a * (float)(pos_a - (kbase + i));
+        if (UPPER) sb[i] = sb[i] * scale_b - slope_b * (float)(pos_b - (kbase + i));
         if (need_mask) {
             const int key = kbase + i;
             if (key > pos_a || (key < lo_a && key >= keep)) sa[i] = -INFINITY;
@@ -130,10 +171,9 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
     const float ma = ceilf(quad_max(fmaxf(fmaxf(sa[0], sa[1]), fmaxf(sa[2], sa[3]))));
     const float na = fmaxf(m[0], ma);
     const float ua = na == -INFINITY ? 0.f : na;                                      // all masked so far
-    const float alpha_a = exp2f(m[0] - ua);
+    alpha_a = exp2f(m[0] - ua);
     m[0] = na;
-    float pa[4], pb[4] = {0.f, 0.f, 0.f, 0.f};
-    float la = 0.f, lb = 0.f, alpha_b = 1.f;
+    float la = 0.f, lb = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         pa[i] = exp2f(sa[i] - ua);
@@ -153,6 +193,7 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
         }
         l[1] = l[1] * alpha_b + lb;
     }
+    }
     const unsigned a0 = pack_bf16(pa[0], pa[1]), a1 = UPPER ? pack_bf16(pb[0], pb[1]) : 0u;
     const unsigned a2 = pack_bf16(pa[2], pa[3]), a3 = UPPER ? pack_bf16(pb[2], pb[3]) : 0u;
     unsigned r0 = 0u, r1 = 0u, r2 = 0u, r3 = 0u;          // what the first rounding left of each probability
@@ -167,7 +208,13 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
         if (UPPER) { r1 = pack_bf16(rb[0], rb[1]); r3 = pack_bf16(rb[2], rb[3]); }
     }
     // the running maximum seldom moves after the first blocks: rescale only when some row's did
-    const bool rescale = __any_sync(0xffffffffu, alpha_a != 1.f || alpha_b != 1.f);
+    // values of this thread's keys kbase .. kbase + 3 that no row of the tile sees (pos_max: the last position of
+    // all 16 rows, which share the value fragments) are taken as zeros: a weight of 0 would not silence a value that
+    // is not a number
+    const int pmax = pos_max;
+    const unsigned vm0 = (kbase <= pmax ? 0x0000ffffu : 0u) | (kbase + 1 <= pmax ? 0xffff0000u : 0u);
+    const unsigned vm1 = (kbase + 2 <= pmax ? 0x0000ffffu : 0u) | (kbase + 3 <= pmax ? 0xffff0000u : 0u);
+    const bool rescale = !SIGMOID && __any_sync(0xffffffffu, alpha_a != 1.f || alpha_b != 1.f);
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) {
         if (rescale) {
@@ -178,14 +225,24 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
                 o[j][3] *= alpha_b;
             }
         }
-        mma_bf16(o[j], a0, a1, a2, a3, f.v[j].x, f.v[j].y);
-        if (PSPLIT) mma_bf16(o[j], r0, r1, r2, r3, f.v[j].x, f.v[j].y);
+        uint2 vv = f.v[j];
+        if (SIGMOID && need_mask) {      // slots behind the last row's position hold whatever the page held before
+            vv.x &= vm0;
+            vv.y &= vm1;
+        }
+        mma_bf16(o[j], a0, a1, a2, a3, vv.x, vv.y);
+        if (PSPLIT) mma_bf16(o[j], r0, r1, r2, r3, vv.x, vv.y);
     }
 }
 
 // an output gate: the result times sigmoid(gate), gate rows `gate_stride` elements apart (null: no gate)
 __device__ __forceinline__ float gate_of(const bf16* __restrict__ gate, size_t at) {
     return gate ? 1.f / (1.f + __expf(-__bfloat162float(gate[at]))) : 1.f;
+}
+// the gate of (token row, head, feature): one number per feature, or one per head
+__device__ __forceinline__ float gate_at(const bf16* __restrict__ gate, size_t row_at, int head, int hd, int d,
+                                         int per_head) {
+    return gate_of(gate, per_head ? row_at + head : row_at + (size_t)head * hd + d);
 }
 
 // ================================ decode: split-KV ==============================================
@@ -223,7 +280,7 @@ __device__ __forceinline__ void cp_async_zfill8(void* smem_dst, const void* src,
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(valid ? 8 : 0));
 }
 
-template <int HD, int DA_STAGES, bool UPPER, bool PSPLIT>
+template <int HD, int DA_STAGES, bool UPPER, bool PSPLIT, bool SIGMOID>
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
@@ -231,7 +288,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
                         const int* __restrict__ kv_span, int slots, int keep, const bf16* __restrict__ gate,
-                        int gate_stride, const float* __restrict__ slopes, const float* __restrict__ sink) {
+                        int gate_stride, const float* __restrict__ slopes, const float* __restrict__ sink,
+                        SigmoidArgs sg) {
     // ring: [stage][piece][128 threads]: HD/16 pieces of 16 bytes for K, then HD/8 pieces of 8 bytes for V;
     // afterwards the same memory serves the merge of the warps ([4 warps][16 rows][HD + 2] floats)
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -349,9 +407,13 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         }
     }
 
-    float o[HD / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    // sigmoid weights: no running maximum; a fixed 0 makes every merge below a plain sum
+    float o[HD / 8][4], m[2] = {SIGMOID ? 0.f : -INFINITY, SIGMOID ? 0.f : -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const float row_scale = SIGMOID ? scale_log2 * query_temperature(pos, sg.temp_coef, sg.temp_every) : scale_log2;
+    const float* bias_a = (SIGMOID && sg.bias && g < G) ? sg.bias + (size_t)(kvh * G + g) * sg.n_dist : nullptr;
+    const float* bias_b = (SIGMOID && sg.bias && UPPER && g + 8 < G) ? sg.bias + (size_t)(kvh * G + g + 8) * sg.n_dist : nullptr;
     // rows g and g+8 are query heads kvh * G + g and + 8
     const float slope_a = (slopes && g < G) ? slopes[kvh * G + g] * LOG2E : 0.f;
     const float slope_b = (slopes && UPPER && g + 8 < G) ? slopes[kvh * G + g + 8] * LOG2E : 0.f;
@@ -373,8 +435,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         for (int j = 0; j < VP; ++j) cur.v[j] = *reinterpret_cast<const uint2*>(ring_mine_v + stage_off + j * 128 * 8);
         issue();                                          // refill the stage just read
         const bool need_mask = (b * 16 + 15 > pos) || (b * 16 < lo);
-        attend_block<HD, UPPER, PSPLIT>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask, keep,
-                                        slope_a, slope_b);
+        attend_block<HD, UPPER, PSPLIT, SIGMOID>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, row_scale, row_scale,
+                                                 need_mask, keep, slope_a, slope_b, bias_a, bias_b, sg.n_dist, pos);
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();                                      // the ring is free: it becomes the merge buffer
@@ -415,8 +477,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         if (used == 1) {
             // a sink: exp(sink) is added to the denominator and to nothing else (base-2 domain here)
             if (sink) L += exp2f(sink[head] * LOG2E - M);
-            out[((size_t)tok * nh + head) * HD + d] =
-                __float2bfloat16_rn(acc / L * gate_of(gate, (size_t)tok * gate_stride + (size_t)head * HD + d));
+            out[((size_t)tok * nh + head) * HD + d] = __float2bfloat16_rn(
+                (SIGMOID ? acc : acc / L) * gate_at(gate, (size_t)tok * gate_stride, head, HD, d, sg.gate_per_head));
         } else {
             const size_t pi = ((size_t)seg * nh + head) * n_splits + split;
             part_o[pi * HD + d] = acc;
@@ -450,8 +512,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             acc += __ldcg(part_o + (p0 + s) * HD + d) * f;
         }
         if (sink) L += exp2f(sink[head] * LOG2E - M);      // once, where the pieces come together
-        out[((size_t)tok * nh + head) * HD + d] =
-            __float2bfloat16_rn(acc / L * gate_of(gate, (size_t)tok * gate_stride + (size_t)head * HD + d));
+        out[((size_t)tok * nh + head) * HD + d] = __float2bfloat16_rn(
+            (SIGMOID ? acc : acc / L) * gate_at(gate, (size_t)tok * gate_stride, head, HD, d, sg.gate_per_head));
     }
 }
 
@@ -459,7 +521,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 // grid (64-token tiles, nkv, G / HPW), 128 threads.  A warp owns 16 consecutive tokens of one
 // request and HPW query heads of one kv group; it walks the 16-key blocks up to its last row's
 // position.  tile_seg / tile_q0 list the tiles (a tile never crosses a request).
-template <int HD, int HPW, bool PSPLIT>
+template <int HD, int HPW, bool PSPLIT, bool SIGMOID>
 __global__ void __launch_bounds__(128)
 prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                          const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
@@ -467,7 +529,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          const int* __restrict__ tile_seg, const int* __restrict__ tile_q0,
                          bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int keep,
                          const bf16* __restrict__ gate, int gate_stride, const float* __restrict__ slopes,
-                         const float* __restrict__ sink) {
+                         const float* __restrict__ sink, SigmoidArgs sg) {
     // Long tiles first: the queries at the end of a prompt have the most keys to read.  Blocks are handed
     // out in the order of blockIdx.x: the (kv head, head pair) blocks of one tile are neighbours there and
     // the tiles go from the longest to the shortest, a greedy schedule by decreasing work.
@@ -505,11 +567,14 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
             qf[h][c] = *reinterpret_cast<const uint4*>(qa + 32 * c);
             qg[h][c] = *reinterpret_cast<const uint4*>(qb + 32 * c);
         }
-        m[h][0] = m[h][1] = -INFINITY;
+        m[h][0] = m[h][1] = SIGMOID ? 0.f : -INFINITY;
         l[h][0] = l[h][1] = 0.f;
 #pragma unroll
         for (int j = 0; j < HD / 8; ++j) o[h][j][0] = o[h][j][1] = o[h][j][2] = o[h][j][3] = 0.f;
     }
+    // rows g and g+8 are tokens at different positions: each has its own temperature
+    const float scale_a = SIGMOID ? scale_log2 * query_temperature(pos_a, sg.temp_coef, sg.temp_every) : scale_log2;
+    const float scale_b = SIGMOID ? scale_log2 * query_temperature(pos_b, sg.temp_coef, sg.temp_every) : scale_log2;
     // with a window that keeps the first keys, their blocks come first, then the walk jumps to the window's
     const int kb = (window > 0 && keep > 0) ? min((keep + 15) / 16, first_block) : 0;
     KVFrag<HD> cur, nxt;
@@ -524,8 +589,10 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 #pragma unroll
         for (int h = 0; h < HPW; ++h) {
             const float slope = slopes ? slopes[head0 + h] * LOG2E : 0.f;       // the rows of a warp are tokens of one head
-            attend_block<HD, true, PSPLIT>(cur, qf[h], qg[h], o[h], m[h], l[h], b * 16, t, pos_a, pos_b, lo_a, lo_b,
-                                           scale_log2, need_mask, keep, slope, slope);
+            const float* bias = (SIGMOID && sg.bias) ? sg.bias + (size_t)(head0 + h) * sg.n_dist : nullptr;
+            attend_block<HD, true, PSPLIT, SIGMOID>(cur, qf[h], qg[h], o[h], m[h], l[h], b * 16, t, pos_a, pos_b, lo_a,
+                                                    lo_b, scale_a, scale_b, need_mask, keep, slope, slope, bias, bias,
+                                                    sg.n_dist, pos_last);
         }
         if (!more) break;
         cur = nxt;
@@ -538,19 +605,21 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
             la += exp2f(sink[head0 + h] * LOG2E - m[h][0]);
             lb += exp2f(sink[head0 + h] * LOG2E - m[h][1]);
         }
-        const float ia = 1.f / la, ib = 1.f / lb;
+        const float ia = SIGMOID ? 1.f : 1.f / la, ib = SIGMOID ? 1.f : 1.f / lb;
         bf16* oa = out + ((size_t)(t0 + q0 + g) * nh + head0 + h) * HD + 2 * t;
         bf16* ob = out + ((size_t)(t0 + q0 + g + 8) * nh + head0 + h) * HD + 2 * t;
-        const size_t ga = (size_t)(t0 + q0 + g) * gate_stride + (size_t)(head0 + h) * HD + 2 * t;
-        const size_t gb = ga + (size_t)8 * gate_stride;
+        const size_t ga = (size_t)(t0 + q0 + g) * gate_stride, gb = ga + (size_t)8 * gate_stride;
+        const int hh = head0 + h, ph = sg.gate_per_head;
 #pragma unroll
         for (int j = 0; j < HD / 8; ++j) {
             if (g < rows)
                 *reinterpret_cast<__nv_bfloat162*>(oa + 8 * j) = __floats2bfloat162_rn(
-                    o[h][j][0] * ia * gate_of(gate, ga + 8 * j), o[h][j][1] * ia * gate_of(gate, ga + 8 * j + 1));
+                    o[h][j][0] * ia * gate_at(gate, ga, hh, HD, 8 * j + 2 * t, ph),
+                    o[h][j][1] * ia * gate_at(gate, ga, hh, HD, 8 * j + 2 * t + 1, ph));
             if (g + 8 < rows)
                 *reinterpret_cast<__nv_bfloat162*>(ob + 8 * j) = __floats2bfloat162_rn(
-                    o[h][j][2] * ib * gate_of(gate, gb + 8 * j), o[h][j][3] * ib * gate_of(gate, gb + 8 * j + 1));
+                    o[h][j][2] * ib * gate_at(gate, gb, hh, HD, 8 * j + 2 * t, ph),
+                    o[h][j][3] * ib * gate_at(gate, gb, hh, HD, 8 * j + 2 * t + 1, ph));
         }
     }
 }
@@ -571,12 +640,13 @@ GESSO_API long long gesso_decode_attention_workspace(int segs, int nh, int nkv, 
     return (long long)segs * nh * n_splits * hd;
 }
 
-GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const void* v_pages,
-                                     const int* block_table, int max_pages, int page_size, const int* positions,
-                                     void* out, int n_segs, int nh, int nkv, int hd,
-                                     int window, float scale, int n_splits, float* part_o, float* part_ml,
-                                     int* tickets, const int* kv_span, int keep, const void* gate, int gate_stride,
-                                     int psplit, const float* slopes, const float* sink, cudaStream_t stream) {
+static int launch_decode(const void* q, const void* k_pages, const void* v_pages,
+                         const int* block_table, int max_pages, int page_size, const int* positions,
+                         void* out, int n_segs, int nh, int nkv, int hd,
+                         int window, float scale, int n_splits, float* part_o, float* part_ml,
+                         int* tickets, const int* kv_span, int keep, const void* gate, int gate_stride,
+                         int psplit, const float* slopes, const float* sink, bool sigmoid, SigmoidArgs sg,
+                         cudaStream_t stream) {
     if (n_segs <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
@@ -599,22 +669,26 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
     const size_t merge = (size_t)4 * 16 * (hd + 2) * sizeof(float);
     const size_t ring = (size_t)stages * (hd / 16 * 16 + hd / 8 * 8) * 128;
     const size_t smem = ring > merge ? ring : merge;
-    const float scale_log2 = scale * LOG2E;
-#define GO4(HD, ST, UP, PS)                                                                                 \
+    const float scale_log2 = sigmoid ? scale : scale * LOG2E;     // sigmoid weights: scores in the natural domain
+#define GO4(HD, ST, UP, PS, SG)                                                                               \
     do {                                                                                                    \
         static bool configured = false;   /* once per instantiation, outside any stream capture */          \
         if (!configured) {                                                                                  \
-            cudaFuncSetAttribute(decode_attention_kernel<HD, ST, UP, PS>,                                   \
+            cudaFuncSetAttribute(decode_attention_kernel<HD, ST, UP, PS, SG>,                               \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
             configured = true;                                                                              \
         }                                                                                                   \
-        launch_pdl(decode_attention_kernel<HD, ST, UP, PS>, grid, dim3(128), smem, stream,                  \
+        launch_pdl(decode_attention_kernel<HD, ST, UP, PS, SG>, grid, dim3(128), smem, stream,              \
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
             page_shift, positions, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,      \
-            tickets, kv_span, slots, keep, (const bf16*)gate, gate_stride, slopes, sink);                   \
+            tickets, kv_span, slots, keep, (const bf16*)gate, gate_stride, slopes, sink, sg);               \
     } while (0)
 #define GO3(HD, ST, UP)                                                                                     \
-    do { if (psplit) GO4(HD, ST, UP, true); else GO4(HD, ST, UP, false); } while (0)
+    do {                                                                                                    \
+        if (sigmoid) GO4(HD, ST, UP, true, true);                                                           \
+        else if (psplit) GO4(HD, ST, UP, true, false);                                                      \
+        else GO4(HD, ST, UP, false, false);                                                                 \
+    } while (0)
 #define GO(HD)                                                                                              \
     do {                                                                                                    \
         if (wide) { if (G > 8) GO3(HD, DA_STAGES_WIDE, true); else GO3(HD, DA_STAGES_WIDE, false); }        \
@@ -630,24 +704,55 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
     return launch_status();
 }
 
-GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const void* v_pages,
-                                      const int* block_table, int max_pages, int page_size, const int* seg_start,
-                                      const int* seg_pos0, const int* tile_seg, const int* tile_q0, int n_tiles,
-                                      void* out, int nh, int nkv, int hd, int window, float scale, int keep,
-                                      const void* gate, int gate_stride, int psplit, const float* slopes,
-                                      const float* sink, cudaStream_t stream) {
+GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const void* v_pages,
+                                     const int* block_table, int max_pages, int page_size, const int* positions,
+                                     void* out, int n_segs, int nh, int nkv, int hd,
+                                     int window, float scale, int n_splits, float* part_o, float* part_ml,
+                                     int* tickets, const int* kv_span, int keep, const void* gate, int gate_stride,
+                                     int psplit, const float* slopes, const float* sink, cudaStream_t stream) {
+    return launch_decode(q, k_pages, v_pages, block_table, max_pages, page_size, positions, out, n_segs, nh, nkv, hd,
+                         window, scale, n_splits, part_o, part_ml, tickets, kv_span, keep, gate, gate_stride, psplit,
+                         slopes, sink, false, SigmoidArgs{nullptr, 0, 0.f, 0, 0}, stream);
+}
+
+// The split-KV kernel with sigmoid weights: dist_bias [nh][n_dist] float32 or null, the queries' temperature, and a
+// gate of one number per head (element [token * gate_stride + head]) or null.  part_ml and tickets as above.
+GESSO_API int gesso_sigmoid_decode_attention(const void* q, const void* k_pages, const void* v_pages,
+                                             const int* block_table, int max_pages, int page_size,
+                                             const int* positions, void* out, int n_segs, int nh, int nkv, int hd,
+                                             int window, float scale, int n_splits, float* part_o, float* part_ml,
+                                             int* tickets, const int* kv_span, const float* dist_bias, int n_dist,
+                                             float temp_coef, int temp_every, const void* gate, int gate_stride,
+                                             cudaStream_t stream) {
+    if (dist_bias && n_dist < 1) return GESSO_ERR_BAD_SIZE;
+    if (gate && gate_stride < nh) return GESSO_ERR_BAD_SIZE;
+    return launch_decode(q, k_pages, v_pages, block_table, max_pages, page_size, positions, out, n_segs, nh, nkv, hd,
+                         window, scale, n_splits, part_o, part_ml, tickets, kv_span, 0, gate, gate_stride, 1, nullptr,
+                         nullptr, true, SigmoidArgs{dist_bias, n_dist, temp_coef, temp_every, 1}, stream);
+}
+
+static int launch_prefill(const void* q, const void* k_pages, const void* v_pages,
+                          const int* block_table, int max_pages, int page_size, const int* seg_start,
+                          const int* seg_pos0, const int* tile_seg, const int* tile_q0, int n_tiles,
+                          void* out, int nh, int nkv, int hd, int window, float scale, int keep,
+                          const void* gate, int gate_stride, int psplit, const float* slopes,
+                          const float* sink, bool sigmoid, SigmoidArgs sg, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
     if ((long long)n_tiles * nh > 2147483647LL) return GESSO_ERR_BAD_SIZE;
-    const float scale_log2 = scale * LOG2E;
-#define GO2(HD, HPW, PS)                                                                                     \
-    prefill_attention_kernel<HD, HPW, PS><<<dim3((unsigned)(n_tiles * nkv * (G / HPW))), 128, 0, stream>>>(  \
+    const float scale_log2 = sigmoid ? scale : scale * LOG2E;     // sigmoid weights: scores in the natural domain
+#define GO2(HD, HPW, PS, SG)                                                                                 \
+    prefill_attention_kernel<HD, HPW, PS, SG><<<dim3((unsigned)(n_tiles * nkv * (G / HPW))), 128, 0, stream>>>(  \
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,       \
         seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, window, scale_log2, keep,               \
-        (const bf16*)gate, gate_stride, slopes, sink)
+        (const bf16*)gate, gate_stride, slopes, sink, sg)
 #define GO(HD, HPW)                                                                                          \
-    do { if (psplit) GO2(HD, HPW, true); else GO2(HD, HPW, false); } while (0)
+    do {                                                                                                     \
+        if (sigmoid) GO2(HD, HPW, true, true);                                                               \
+        else if (psplit) GO2(HD, HPW, true, false);                                                          \
+        else GO2(HD, HPW, false, false);                                                                     \
+    } while (0)
     if (hd <= 64 && G % 2 == 0) {
         if (hd == 32) GO(32, 2); else GO(64, 2);
     } else {
@@ -656,4 +761,30 @@ GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const 
 #undef GO
 #undef GO2
     return launch_status();
+}
+
+GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const void* v_pages,
+                                      const int* block_table, int max_pages, int page_size, const int* seg_start,
+                                      const int* seg_pos0, const int* tile_seg, const int* tile_q0, int n_tiles,
+                                      void* out, int nh, int nkv, int hd, int window, float scale, int keep,
+                                      const void* gate, int gate_stride, int psplit, const float* slopes,
+                                      const float* sink, cudaStream_t stream) {
+    return launch_prefill(q, k_pages, v_pages, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0,
+                          n_tiles, out, nh, nkv, hd, window, scale, keep, gate, gate_stride, psplit, slopes, sink, false,
+                          SigmoidArgs{nullptr, 0, 0.f, 0, 0}, stream);
+}
+
+// The flash kernel with sigmoid weights (see gesso_sigmoid_decode_attention for the arguments beside the softmax's).
+GESSO_API int gesso_sigmoid_prefill_attention(const void* q, const void* k_pages, const void* v_pages,
+                                              const int* block_table, int max_pages, int page_size,
+                                              const int* seg_start, const int* seg_pos0, const int* tile_seg,
+                                              const int* tile_q0, int n_tiles, void* out, int nh, int nkv, int hd,
+                                              int window, float scale, const float* dist_bias, int n_dist,
+                                              float temp_coef, int temp_every, const void* gate, int gate_stride,
+                                              cudaStream_t stream) {
+    if (dist_bias && n_dist < 1) return GESSO_ERR_BAD_SIZE;
+    if (gate && gate_stride < nh) return GESSO_ERR_BAD_SIZE;
+    return launch_prefill(q, k_pages, v_pages, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0,
+                          n_tiles, out, nh, nkv, hd, window, scale, 0, gate, gate_stride, 1, nullptr, nullptr, true,
+                          SigmoidArgs{dist_bias, n_dist, temp_coef, temp_every, 1}, stream);
 }

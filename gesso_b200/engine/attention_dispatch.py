@@ -38,16 +38,7 @@ def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=
     if q.dtype == torch.bfloat16 and vd == hd and ops.fast_attention_takes(hd, page_size, nh, nkv):
         if ctx.decode_only:
             splits = ops.decode_splits(ctx.n_segs, nkv, ctx.max_kv_len, uneven=True)
-            ws = None
-            if splits > 1:
-                key = ("decode_attention_workspace", ctx.n_segs, nh, nkv, hd, splits)
-                ws = rt.shared.get(key)
-                if ws is None:
-                    dev = q.device
-                    ws = (torch.empty((ctx.n_segs * nh * splits * hd,), dtype=torch.float32, device=dev),
-                          torch.empty((ctx.n_segs * nh * splits * 2,), dtype=torch.float32, device=dev),
-                          torch.zeros((ctx.n_segs * nkv,), dtype=torch.int32, device=dev))
-                    rt.shared[key] = ws
+            ws = _decode_workspace(rt, q, ctx, nh, nkv, hd, splits) if splits > 1 else None
             return ops.decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                         window, scale, splits, ws, ctx.kv_span, keep_first, gate, split_weights,
                                         slopes=slopes, sink=sink)
@@ -63,9 +54,36 @@ def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=
                                        ctx.positions, ctx.seg_of_token, window, scale, keep_first, gate)
 
 
+def _decode_workspace(rt, q, ctx, nh, nkv, hd, splits):
+    key = ("decode_attention_workspace", ctx.n_segs, nh, nkv, hd, splits)
+    ws = rt.shared.get(key)
+    if ws is None:
+        dev = q.device
+        ws = (torch.empty((ctx.n_segs * nh * splits * hd,), dtype=torch.float32, device=dev),
+              torch.empty((ctx.n_segs * nh * splits * 2,), dtype=torch.float32, device=dev),
+              torch.zeros((ctx.n_segs * nkv,), dtype=torch.int32, device=dev))
+        rt.shared[key] = ws
+    return ws
+
+
 def sigmoid_attention(rt, q, cache, ctx, scale, dist_bias=None, temp_coef: float = 0.0, temp_every: int = 0, gate=None,
                       window=None):
-    """Attention with sigmoid weights (no softmax) of the step's queries over the paged cache.  float32 runs and
-    sizes the tensor-core kernels do not take run the FP32-arithmetic kernel."""
+    """Attention with sigmoid weights (no softmax) of the step's queries over the paged cache.  bfloat16 runs take
+    the tensor-core kernels when the sizes fit them (head 32/64/96/128, values as wide as keys, pages in multiples
+    of 16 slots): the split-KV kernel for steps of single tokens, the flash kernel for steps with portions, each
+    weight in two bfloat16 pieces.  float32 runs and other sizes run the FP32-arithmetic kernel."""
+    N, nh, hd = q.shape
+    nkv, page_size = cache.k_pages.shape[1], cache.k_pages.shape[2]
+    vd = cache.v_pages.shape[2]
+    if (q.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16 and vd == hd
+            and ops.fast_attention_takes(hd, page_size, nh, nkv)):
+        if ctx.decode_only:
+            splits = ops.decode_splits(ctx.n_segs, nkv, ctx.max_kv_len, uneven=True)
+            ws = _decode_workspace(rt, q, ctx, nh, nkv, hd, splits) if splits > 1 else None
+            return ops.sigmoid_decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, scale,
+                                                splits, ws, ctx.kv_span, dist_bias, temp_coef, temp_every, gate, window)
+        return ops.sigmoid_prefill_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
+                                             ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, scale, dist_bias, temp_coef,
+                                             temp_every, gate, window)
     return ops.sigmoid_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                          ctx.seg_of_token, scale, dist_bias, temp_coef, temp_every, gate, window)

@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -827,19 +827,32 @@ def gated_rmsnorm(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch
     return out
 
 
-_lib.declare("gesso_gla", [_lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.F, _lib.F, _lib.P, _lib.LL, _lib.P, _lib.P, _lib.P,
-                            _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P])
+_lib.declare("gesso_gla", [_lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.F, _lib.F, _lib.P, _lib.LL, _lib.P, _lib.P, _lib.P,
+                            _lib.P, _lib.I, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P])
 _lib.declare("gesso_head_gated_rmsnorm", [_lib.P, _lib.P, _lib.F, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I,
                                            _lib.I, _lib.P])
+
+# Steps whose longest portion has at least this many tokens run the gated recurrence by 64-token tiles side by side
+# (three launches, each tile walked twice) instead of token after token (GESSO_GLA_CHUNK_MIN_TOKENS; a huge number
+# keeps every step on the walk).
+GLA_CHUNK_MIN_TOKENS = int(os.environ.get("GESSO_GLA_CHUNK_MIN_TOKENS", "256"))
+
+
+def gla_chunked_takes(longest_portion: int) -> bool:
+    return longest_portion >= GLA_CHUNK_MIN_TOKENS
 
 
 def gated_linear_attention(proj: torch.Tensor, z: torch.Tensor, z_bias: Optional[torch.Tensor], tau: float,
                            q_scale: float, state: torch.Tensor, seg_start: torch.Tensor, slots: torch.Tensor,
-                           n_segs: int, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
+                           n_segs: int, n_heads: int, dim: int, vdim: int, tile_seg: Optional[torch.Tensor] = None,
+                           tile_q0: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Linear attention with a decay per key channel and token, as a recurrence: ``a = sigmoid(z + z_bias) ** (1 /
-    tau)``, ``S = diag(a) S + k v^T``, ``o = S^T (q_scale * q)`` with q, k, v the columns of ``proj`` [N, >= 2*H*D +
-    H*Dv] (q, then k, then v, head by head) and ``z`` [N, H*D] float32.  ``state``: [slots, H, Dv, D] float32, read at
-    a segment's start and left as its last token makes it.  Returns o [N, H * Dv] float32."""
+    tau)``, ``S = diag(a) S + k v^T``, ``o = q_scale * S^T q`` with q, k, v the columns of ``proj`` [N, >= 2*H*D +
+    H*Dv] (q, then k, then v, head by head) and ``z`` [N, H*D] float32.
+    ``state``: [slots, H, Dv, D] float32, read at a segment's start and left as its last token makes it.  With
+    ``tile_seg`` / ``tile_q0`` (the step's 64-token tiles: segment and first token, as the step's metadata lists
+    them) the tiles run side by side: every tile's own sum, a walk over each request's tiles that hands every tile
+    the state it starts from, then every tile's outputs.  Returns o [N, H * Dv] float32."""
     _need(proj.is_cuda and proj.dim() == 2 and proj.stride(1) == 1, "proj must be rows on the device")
     H, D, Dv = int(n_heads), int(dim), int(vdim)
     N = proj.shape[0]
@@ -854,8 +867,17 @@ def gated_linear_attention(proj: torch.Tensor, z: torch.Tensor, z_bias: Optional
     _cuda_contig(seg_start, "seg_start", torch.int32)
     _cuda_contig(slots, "slots", torch.int32)
     out = torch.empty((N, H * Dv), dtype=torch.float32, device=proj.device)
-    _lib.check(_lib.library().gesso_gla(_p(proj), _dt(proj), int(proj.stride(0)), _p(z), _p(z_bias), float(tau),
-                                        float(q_scale), _p(state), state.stride(0), _p(seg_start), _p(slots), _p(out), N,
+    decay = torch.empty_like(z)
+    n_tiles, ws, ws_decay = 0, None, None
+    if tile_seg is not None:
+        _cuda_contig(tile_seg, "tile_seg", torch.int32)
+        _cuda_contig(tile_q0, "tile_q0", torch.int32)
+        n_tiles = tile_seg.numel()
+        ws = torch.empty((max(n_tiles, 1) * H * Dv * D,), dtype=torch.float32, device=proj.device)
+        ws_decay = torch.empty((max(n_tiles, 1) * H * D,), dtype=torch.float32, device=proj.device)
+    _lib.check(_lib.library().gesso_gla(_p(proj), _dt(proj), int(proj.stride(0)), _p(z), _p(z_bias), _p(decay),
+                                        float(tau), float(q_scale), _p(state), state.stride(0), _p(seg_start), _p(slots),
+                                        _p(tile_seg), _p(tile_q0), n_tiles, _p(ws), _p(ws_decay), _p(out), N,
                                         int(n_segs), H, D, Dv, _stream()), "gated_linear_attention")
     return out
 
@@ -1323,6 +1345,85 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
         float(scale), int(keep_first or 0), _p(gate), gate_stride, 1 if split_weights else 0, _p(slopes), _p(sink), _stream()),
         "prefill_attention")
+    return out
+
+
+_lib.declare("gesso_sigmoid_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
+                                                _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
+                                                _lib.P, _lib.P, _lib.P, _lib.I, _lib.F, _lib.I, _lib.P, _lib.I, _lib.P])
+_lib.declare("gesso_sigmoid_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
+                                                 _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.P,
+                                                 _lib.I, _lib.F, _lib.I, _lib.P, _lib.I, _lib.P])
+
+
+def _check_sigmoid_extras(dist_bias, gate, rows: int, nh: int, dtype) -> Tuple[int, int]:
+    n_dist = 0
+    if dist_bias is not None:
+        _cuda_contig(dist_bias, "dist_bias", torch.float32)
+        _need(dist_bias.dim() == 2 and dist_bias.shape[0] == nh, "dist_bias must be [heads, distances]")
+        n_dist = dist_bias.shape[1]
+    gate_stride = 0
+    if gate is not None:
+        _need(gate.is_cuda and gate.dim() == 2 and tuple(gate.shape) == (rows, nh) and gate.stride(1) == 1
+              and gate.dtype == dtype, "gate must be [rows, heads] of the pages' type with unit column stride")
+        gate_stride = int(gate.stride(0))
+    return n_dist, gate_stride
+
+
+def sigmoid_decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                             positions: torch.Tensor, scale: float, n_splits: int, workspace=None,
+                             kv_span: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None,
+                             temp_coef: float = 0.0, temp_every: int = 0, gate: Optional[torch.Tensor] = None,
+                             window: Optional[int] = None) -> torch.Tensor:
+    """Split-KV attention with sigmoid weights for a step of single tokens on the tensor cores (bfloat16; sizes as
+    :func:`fast_attention_takes`, values as wide as keys): the weights as :func:`sigmoid_attention_generic` defines
+    them, each fed to the product with the values as two bfloat16 pieces; the pieces of a split add up.
+    ``workspace`` and ``kv_span`` as for :func:`decode_attention`."""
+    _cuda_contig(q, "q", torch.bfloat16)
+    S, nh, hd = q.shape
+    nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    _need(k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16, "cache pages must be bfloat16")
+    n_dist, gate_stride = _check_sigmoid_extras(dist_bias, gate, S, nh, q.dtype)
+    if kv_span is not None:
+        _cuda_contig(kv_span, "kv_span", torch.int32)
+        _need(kv_span.numel() == 2, "kv_span holds two numbers")
+    out = torch.empty((S, nh * hd), dtype=q.dtype, device=q.device)
+    if n_splits > 1:
+        if workspace is None:
+            workspace = (torch.empty((S * nh * n_splits * hd,), dtype=torch.float32, device=q.device),
+                         torch.empty((S * nh * n_splits * 2,), dtype=torch.float32, device=q.device),
+                         torch.zeros((S * nkv,), dtype=torch.int32, device=q.device))
+        part_o, part_ml, tickets = workspace
+        _need(part_o.numel() >= S * nh * n_splits * hd and part_ml.numel() >= S * nh * n_splits * 2
+              and tickets.numel() >= S * nkv, "split-KV workspace is too small")
+    else:
+        part_o = part_ml = tickets = None
+    _lib.check(_lib.library().gesso_sigmoid_decode_attention(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(positions),
+        _p(out), S, nh, nkv, hd, int(window or 0), float(scale), int(n_splits), _p(part_o), _p(part_ml), _p(tickets),
+        _p(kv_span), _p(dist_bias), n_dist, float(temp_coef), int(temp_every), _p(gate), gate_stride, _stream()),
+        "sigmoid_decode_attention")
+    return out
+
+
+def sigmoid_prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                              seg_start: torch.Tensor, seg_pos0: torch.Tensor, tile_seg: torch.Tensor,
+                              tile_q0: torch.Tensor, scale: float, dist_bias: Optional[torch.Tensor] = None,
+                              temp_coef: float = 0.0, temp_every: int = 0, gate: Optional[torch.Tensor] = None,
+                              window: Optional[int] = None) -> torch.Tensor:
+    """Attention with sigmoid weights for a step with prompt portions on the tensor cores (bfloat16; the step's
+    64-token query tiles; sizes and weights as for :func:`sigmoid_decode_attention`)."""
+    _cuda_contig(q, "q", torch.bfloat16)
+    N, nh, hd = q.shape
+    nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    _need(k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16, "cache pages must be bfloat16")
+    n_dist, gate_stride = _check_sigmoid_extras(dist_bias, gate, N, nh, q.dtype)
+    out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
+    _lib.check(_lib.library().gesso_sigmoid_prefill_attention(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(seg_start),
+        _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
+        float(scale), _p(dist_bias), n_dist, float(temp_coef), int(temp_every), _p(gate), gate_stride, _stream()),
+        "sigmoid_prefill_attention")
     return out
 
 

@@ -92,8 +92,10 @@ class GatedLinearAttention(Mixer):
         a0 = g0 + H * Dv
         inner = proj[:, a0:a0 + self.rank].contiguous()
         z = ops.linear(inner, self.w_a2, out_dtype=torch.float32)          # the decay's logits, float32 from here on
+        # long prompt portions: the step's 64-token tiles side by side instead of token after token
+        tiles = (ctx.tile_seg, ctx.tile_q0) if not ctx.decode_only and ops.gla_chunked_takes(ctx.max_seg_len) else (None, None)
         o = ops.gated_linear_attention(proj, z, self.b_a2, self.tau, self.q_scale, cache.state, ctx.seg_start,
-                                       cache.slots, ctx.n_segs, H, D, Dv)
+                                       cache.slots, ctx.n_segs, H, D, Dv, *tiles)
         y = ops.head_gated_rmsnorm(o, self.w_norm, self.eps, proj[:, g0:g0 + H * Dv], H, x.dtype, gate_act="silu")
         return ops.linear(y, self.w_o, out_dtype=torch.float32), None
 

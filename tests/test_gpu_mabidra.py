@@ -183,7 +183,9 @@ def _bias_by_distance(rel, hb, n_max, bias_max):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,Vd,B,bias_max,every", [(4, 2, 16, 24, 12, 40.0, 8), (3, 3, 10, 40, 6, 9.5, 1),
                                                        (8, 1, 64, 64, 32, 250.0, 64), (2, 1, 96, 32, 20, 33.0, 50),
-                                                       (1, 1, 48, 48, 2, 500.0, 7), (6, 2, 128, 128, 16, 128.0, 100)])
+                                                       (1, 1, 48, 48, 2, 500.0, 7), (6, 2, 128, 128, 16, 128.0, 100),
+                                                       (4, 2, 32, 32, 10, 64.0, 3), (12, 1, 96, 96, 8, 300.0, 128),
+                                                       (32, 2, 64, 64, 6, 20.0, 16)])
 def test_sigmoid_attention_far_keys_table_rows_and_temperature(H, G, D, Vd, B, bias_max, every, dtype):
     """One sequence of 300 positions in pages handed out of order, free pages full of NaN.  Head 0 is quiet (a per-head
     number of -12 closes every key) except for keys made to stand out: the first token, a token hundreds back and the
@@ -234,6 +236,29 @@ def test_sigmoid_attention_far_keys_table_rows_and_temperature(H, G, D, Vd, B, b
                                             every, gate[i:i + 1]).double().cpu()
         err = (got[0] - want[i]).abs().max() / want.abs().max()
         assert err <= tol, f"single token at {i}: {float(err):.3e}"
+    if dtype == torch.bfloat16 and D == Vd and ops.fast_attention_takes(D, page, H, G):
+        # the tensor-core kernels: the whole sequence as one portion, a portion that starts inside a page and a tile,
+        # and single tokens with the keys in one piece and cut into several
+        def tiles_of(n):
+            return i32([0] * ((n + 63) // 64)), i32(list(range(0, n, 64)))
+        for first in (0, 100, 293):
+            n = T - first
+            tile_seg, tile_q0 = tiles_of(n)
+            got = ops.sigmoid_prefill_attention(q[first:].contiguous(), kp, vp, bt, i32([0, n]), i32([first]), tile_seg,
+                                                tile_q0, scale, table, coef, every, gate[first:]).double().cpu()
+            err = (got - want[first:]).abs().max(dim=1).values / want.abs().max()
+            assert err.max() <= tol, (f"tensor-core portion from {first}: {float(err.max()):.3e} first at "
+                                      f"{first + int((err > tol).nonzero()[0])}")
+        for i in probes + (0, 1, 15, 16, B // 2, wall + 3, min(T - 2, int(bias_max)), min(T - 1, int(bias_max) + 1)):
+            for splits in (1, 3):
+                got = ops.sigmoid_decode_attention(q[i:i + 1].contiguous(), kp, vp, bt, pos[i:i + 1], scale, splits, None,
+                                                   None, table, coef, every, gate[i:i + 1]).double().cpu()
+                err = (got[0] - want[i]).abs().max() / want.abs().max()
+                assert err <= tol, f"tensor-core single token at {i}, {splits} pieces: {float(err):.3e}"
+        got = ops.sigmoid_prefill_attention(q, kp, vp, bt, i32([0, T]), i32([0]), *tiles_of(T), scale).double().cpu()
+        bare = pb.sigmoid_attend_fast(q.double().cpu(), k.double().cpu(), v.double().cpu(), scale,
+                                      torch.zeros(2, H, dtype=pb.F64), torch.zeros(H, dtype=pb.F64), 4.0, H // G)
+        assert (got - bare.reshape(T, H * Vd)).abs().max() <= tol * bare.abs().max()
     # no table, no temperature, no gate: every weight is the sigmoid of the scaled product
     plainest = pb.sigmoid_attend_fast(q.double().cpu(), k.double().cpu(), v.double().cpu(), scale,
                                       torch.zeros(2, H, dtype=pb.F64), torch.zeros(H, dtype=pb.F64), 4.0, H // G)
@@ -243,7 +268,7 @@ def test_sigmoid_attention_far_keys_table_rows_and_temperature(H, G, D, Vd, B, b
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,D,Dv,tau", [(2, 16, 24, 4.0), (3, 40, 8, 1.0), (1, 64, 64, 16.0), (2, 128, 20, 8.0),
-                                        (1, 200, 33, 2.0), (4, 7, 5, 32.0)])
+                                        (1, 200, 33, 2.0), (4, 7, 5, 32.0), (2, 128, 128, 16.0), (2, 64, 256, 4.0)])
 def test_gated_recurrence_portions_and_single_tokens(H, D, Dv, tau, dtype):
     """Decays per key channel and token: channel 0 of head 0 forgets nothing (a logit of +30) and carries the first
     token, made large, to the last of 300 positions; channel 1 forgets everything (-30 under any tau here) although it
@@ -251,7 +276,7 @@ def test_gated_recurrence_portions_and_single_tokens(H, D, Dv, tau, dtype):
     one portion, token by token, and in uneven portions beside another request; the state slot carries everything."""
     from gesso_b200 import ops
     T = 300
-    stride = 2 * H * D + H * Dv + 11
+    stride = 2 * H * D + H * Dv + (16 if Dv >= 128 else 11)       # rows on 16-byte boundaries, and not
     q_scale = float(D) ** -0.5
     rows = [torch.randn(T, stride, device=DEV).to(dtype) for _ in range(2)]
     zs = [(2.0 + 3.0 * torch.randn(T, H * D, device=DEV)) for _ in range(2)]
@@ -304,6 +329,31 @@ def test_gated_recurrence_portions_and_single_tokens(H, D, Dv, tau, dtype):
         at += n
     for r in range(2):
         check(torch.cat(got[r]), r, f"portions, request {r}")
+    # by 64-token tiles side by side: one portion from an empty state, then two requests' uneven portions, the later
+    # ones from the state the earlier ones left
+    def tiles_of(lens):
+        return (i32([s for s, n in enumerate(lens) for _ in range(0, n, 64)]),
+                i32([x for n in lens for x in range(0, n, 64)]))
+    state[0].zero_()
+    check(ops.gated_linear_attention(rows[0], zs[0], zb, tau, q_scale, state, i32([0, T]), i32([0]), 1, H, D, Dv,
+                                     *tiles_of([T])).double().cpu(), 0, "one portion by tiles")
+    assert (state[0].double().cpu() - last[0]).abs().max() <= tol * last[0].abs().max()
+    state[0].zero_()
+    state[1].zero_()
+    got, at = [[], []], [0, 0]
+    for lens in ([130, 64], [1, 171], [169, 65]):
+        both = torch.cat([rows[r][at[r]:at[r] + n] for r, n in enumerate(lens)])
+        zboth = torch.cat([zs[r][at[r]:at[r] + n] for r, n in enumerate(lens)]).contiguous()
+        _, start = segments(lens)
+        y = ops.gated_linear_attention(both, zboth, zb, tau, q_scale, state, start, i32([1, 0]), 2, H, D, Dv, *tiles_of(lens))
+        got[0].append(y[:lens[0]].double().cpu())
+        got[1].append(y[lens[0]:].double().cpu())
+        at = [at[0] + lens[0], at[1] + lens[1]]
+    assert at == [T, T]
+    for r in range(2):
+        check(torch.cat(got[r]), r, f"portions by tiles, request {r}")
+    assert (state[1].double().cpu() - last[0]).abs().max() <= tol * last[0].abs().max()
+    assert (state[0].double().cpu() - last[1]).abs().max() <= tol * last[1].abs().max()
     # without a bias vector
     state[0].zero_()
     y = ops.gated_linear_attention(rows[0], zs[0] + zb, None, tau, q_scale, state, i32([0, T]), i32([0]), 1, H, D, Dv)
