@@ -125,6 +125,16 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
                                              const float* __restrict__ bias_a = nullptr,
                                              const float* __restrict__ bias_b = nullptr, int n_dist = 0,
                                              int pos_max = 0) {
+    // the table's entries of this thread's keys are asked for ahead of the score products, which hide the reads
+    float ba[4] = {0.f, 0.f, 0.f, 0.f}, bb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (SIGMOID) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = key0 + 4 * t + i;
+            if (bias_a) ba[i] = __ldg(bias_a + min(max(pos_a - key, 0), n_dist - 1));
+            if (UPPER && bias_b) bb[i] = __ldg(bias_b + min(max(pos_b - key, 0), n_dist - 1));
+        }
+    }
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
@@ -143,13 +153,11 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int key = kbase + i;
-            float xa = sa[i] * scale_a, xb = sb[i] * scale_b;
-            if (bias_a) xa += __ldg(bias_a + min(max(pos_a - key, 0), n_dist - 1));
-            if (UPPER && bias_b) xb += __ldg(bias_b + min(max(pos_b - key, 0), n_dist - 1));
+            const float xa = fmaf(sa[i], scale_a, ba[i]), xb = fmaf(sb[i], scale_b, bb[i]);
             const bool on_a = !need_mask || (key <= pos_a && (key >= lo_a || key < keep));
             const bool on_b = UPPER && (!need_mask || (key <= pos_b && (key >= lo_b || key < keep)));
-            pa[i] = on_a ? 1.f / (1.f + __expf(-xa)) : 0.f;
-            pb[i] = on_b ? 1.f / (1.f + __expf(-xb)) : 0.f;
+            pa[i] = on_a ? __fdividef(1.f, 1.f + __expf(-xa)) : 0.f;
+            pb[i] = on_b ? __fdividef(1.f, 1.f + __expf(-xb)) : 0.f;
         }
     } else {
 #pragma unroll
