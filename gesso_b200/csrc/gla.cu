@@ -18,8 +18,8 @@
 //     and hands every tile the state it starts from; OUTS walks every tile again from that state and reads out.
 //     A tile's tokens are walked twice (1.5 times the arithmetic of one walk), but all tiles at once.
 // The columns of S are independent: a thread owns two value columns and 16 key features of them (32 state
-// values in registers; L lanes side by side cover a column's D features, zeros behind D), the read-out is summed
-// over those lanes by shuffles.  A tile of tokens' q, k (run type), a and v (float32) is staged through shared
+// values in registers; L lanes side by side cover a column's D features, four features a lane in turn, zeros
+// behind D), the read-out is summed over those lanes by shuffles.  A tile of tokens' q, k (run type), a and v (float32) is staged through shared
 // memory at a time, by 16-byte loads where the sizes allow.
 // The state is stored [slot][head][value column][feature], as the fixed-decay recurrence stores it.
 // These kernels do not let their successor in before they end: each reads what kernels further back than its
@@ -78,7 +78,9 @@ gla_kernel(const T* __restrict__ proj, int row_stride, const float* __restrict__
     const int h = blockIdx.y, c0 = blockIdx.z * COLS;
     const int cw = threadIdx.x / L, part = threadIdx.x % L;
     const int col = c0 + GLA_CPT * cw;                // this thread's columns col, col + 1
-    const int d0 = part * GLA_PER_LANE;               // this lane's features d0 .. d0 + 15
+    // this lane's 16 features, four at a time: piece r = 0 .. 3 is features 4 (r L + part) .. + 3, so that the L
+    // lanes of a column read consecutive 16 bytes of a staged row (no two of them on one bank)
+    auto feat = [&](int i) { return 4 * ((i >> 2) * L + part) + (i & 3); };
     int t0, n;
     float* st;                                        // where the walk starts from (WALK, OUTS) and what it leaves (WALK, SUMS)
     if (MODE == GLA_WALK) {
@@ -97,7 +99,7 @@ gla_kernel(const T* __restrict__ proj, int row_stride, const float* __restrict__
     for (int c = 0; c < GLA_CPT; ++c)
 #pragma unroll
         for (int i = 0; i < GLA_PER_LANE; ++i)
-            S[c][i] = (MODE != GLA_SUMS && col + c < Dv && d0 + i < D) ? st[(size_t)(col + c) * D + d0 + i] : 0.f;
+            S[c][i] = (MODE != GLA_SUMS && col + c < Dv && feat(i) < D) ? st[(size_t)(col + c) * D + feat(i)] : 0.f;
     // SUMS: the lanes of the block's first column, in the first group of columns, also keep the product of the decays
     const bool track = MODE == GLA_SUMS && blockIdx.z == 0 && cw == 0;
     float P[GLA_PER_LANE];
@@ -150,9 +152,9 @@ gla_kernel(const T* __restrict__ proj, int row_stride, const float* __restrict__
 #pragma unroll
             for (int r = 0; r < GLA_PER_LANE / 4; ++r) {
                 float kk[4], qq[4], aa[4];
-                load4(sa + (size_t)i * DP + d0 + 4 * r, aa);
-                load4(sk + (size_t)i * DP + d0 + 4 * r, kk);
-                if (MODE != GLA_SUMS) load4(sq + (size_t)i * DP + d0 + 4 * r, qq);
+                load4(sa + (size_t)i * DP + 4 * (r * L + part), aa);
+                load4(sk + (size_t)i * DP + 4 * (r * L + part), kk);
+                if (MODE != GLA_SUMS) load4(sq + (size_t)i * DP + 4 * (r * L + part), qq);
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
                     S[0][4 * r + x] = fmaf(aa[x], S[0][4 * r + x], kk[x] * v.x);
@@ -183,12 +185,12 @@ gla_kernel(const T* __restrict__ proj, int row_stride, const float* __restrict__
         for (int c = 0; c < GLA_CPT; ++c)
 #pragma unroll
             for (int i = 0; i < GLA_PER_LANE; ++i)
-                if (col + c < Dv && d0 + i < D) st[(size_t)(col + c) * D + d0 + i] = S[c][i];
+                if (col + c < Dv && feat(i) < D) st[(size_t)(col + c) * D + feat(i)] = S[c][i];
     }
     if (MODE == GLA_SUMS && track) {
 #pragma unroll
         for (int i = 0; i < GLA_PER_LANE; ++i)
-            if (d0 + i < D) ws_decay[((size_t)blockIdx.x * H + h) * D + d0 + i] = P[i];
+            if (feat(i) < D) ws_decay[((size_t)blockIdx.x * H + h) * D + feat(i)] = P[i];
     }
 }
 
