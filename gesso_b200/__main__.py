@@ -119,11 +119,18 @@ def _check() -> int:
                                                "mask": {"size": 12}}, "mlp": moe},
         {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.18, "conv": 3, "v_mix": True,
                                         "mask": {"size": 10}}, "mlp": moe}]}
+    mmoe = {"kind": "moe", "expert": {"ff": 48}, "router": {"experts": 6, "top": 2}}
+    mabidra = {"architecture": "Mabidra", "vocab": 320, "width": 128, "embedding": {"scale": 0.5},
+               "norm": {"eps": 1e-6, "groups": 4}, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": [
+        {"type": "gla", "mixer": {"heads": 2, "dim": 32, "vdim": 48, "tau": 8.0}, "mlp": {"kind": "dense", "ff": 192}},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.18, "bias_max": 24,
+                                        "q_temp": {"coef": 0.3, "every": 8}}, "mlp": mmoe},
+        {"type": "gla", "mixer": {"heads": 2, "dim": 32, "vdim": 32, "tau": 2.0}, "mlp": mmoe}]}
     prompts = [[5, 17, 3, 250, 9, 77, 41], [1] * 19, [300]]
     # a mixture of experts may choose another expert on a close call in bfloat16, which moves the logits by more
     # than rounding: its decoding is held to a whole run in float32 only
     for cfg, runs in ((lfm2, (("float32", 1e-4), ("bfloat16", 0.0625))), (sodurax, (("float32", 1e-4), ("bfloat16", None))),
-                      (memipel, (("float32", 1e-4), ("bfloat16", None)))):
+                      (memipel, (("float32", 1e-4), ("bfloat16", None))), (mabidra, (("float32", 1e-4), ("bfloat16", None)))):
         with tempfile.TemporaryDirectory() as d:
             write_random_model(d, cfg, 0, style="fan_in")
             for dtype, slack in runs:

@@ -481,6 +481,23 @@ def test_replay_matches_plain(name, schedule, dtype, loaded, plain, tmp_path):
     compare(rows, ref, tol_of(name, dtype), f"{name}/{schedule}/{dtype}", plain.margins(name, dtype))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("schedule", ["whole", "portions", "mixed"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_recurrence_by_tiles_in_the_engine(name, schedule, dtype, loaded, plain, tmp_path, monkeypatch):
+    """With the threshold lowered, every step whose longest portion has 65 tokens or more runs the recurrence by
+    64-token tiles (tile sums, scan, tile outputs) instead of token after token: portions that start from the state
+    an earlier portion left, beside single tokens of other requests, on slots that are used again."""
+    from gesso_b200 import ops
+    monkeypatch.setattr(ops, "GLA_CHUNK_MIN_TOKENS", 65)
+    reqs, ref = plain(name)
+    tb, max_tokens = SCHEDULES[schedule](reqs)
+    model = loaded(name, dtype)
+    tt.run_in_process(model, tb, max_tokens, str(tmp_path))
+    rows = tt.read_rows(tb, str(tmp_path), model.vocab_size)
+    compare(rows, ref, tol_of(name, dtype), f"tiles {name}/{schedule}/{dtype}", plain.margins(name, dtype))
+
+
 @pytest.mark.parametrize("sizes", [(2,), (3, 2), (2, 2, 2, 5), (64, 2, 63), (16, 17, 15, 2)])
 def test_portions_of_every_size_float32(sizes, loaded, plain, tmp_path):
     """Portions down to two tokens, and cuts on and beside page borders, give the logits of whole prompts."""
