@@ -43,12 +43,13 @@ __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) -
 
 __global__ void __launch_bounds__(256)
 gla_decay_kernel(const float* __restrict__ z, const float* __restrict__ z_bias, float inv_tau, float* __restrict__ decay,
-                 long long n, int HD) {
+                 int HD) {
     pdl_wait();
-    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
-    if (i >= n) return;
+    const int j = blockIdx.y * 256 + threadIdx.x;          // grid: (tokens, blocks of 256 key channels)
+    if (j >= HD) return;
+    const size_t i = (size_t)blockIdx.x * HD + j;
     float zz = z[i];
-    if (z_bias) zz += z_bias[i % HD];
+    if (z_bias) zz += z_bias[j];
     decay[i] = expf(log_sigmoid_f(zz) * inv_tau);
 }
 
@@ -218,11 +219,25 @@ gla_chunk_scan_kernel(float* __restrict__ state, long long slot_stride, const in
     const int d = e % D;
     float* st = state + (size_t)slots[seg] * slot_stride + (size_t)h * Dv * D + e;
     float S = *st;
-    for (int c = 0; c * GLA_CHUNK < n; ++c) {
-        float* u = ws + ((size_t)(first + c) * H + h) * Dv * D + e;
-        const float U = *u;
-        *u = S;
-        S = fmaf(ws_decay[((size_t)(first + c) * H + h) * D + d], S, U);
+    const int nt = (n + GLA_CHUNK - 1) / GLA_CHUNK;
+    const size_t tile_stride = (size_t)H * Dv * D, decay_stride = (size_t)H * D;
+    float* u = ws + ((size_t)first * H + h) * Dv * D + e;
+    const float* a = ws_decay + ((size_t)first * H + h) * D + d;
+    // four tiles' sums and decays are read ahead of the chain of dependent products
+    for (int c = 0; c < nt; c += 4) {
+        float U[4], A[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (c + k < nt) {
+                U[k] = u[(size_t)(c + k) * tile_stride];
+                A[k] = a[(size_t)(c + k) * decay_stride];
+            }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (c + k < nt) {
+                u[(size_t)(c + k) * tile_stride] = S;
+                S = fmaf(A[k], S, U[k]);
+            }
     }
     *st = S;
 }
@@ -254,10 +269,9 @@ GESSO_API int gesso_gla(const void* proj, int dtype, int row_stride, const float
     const size_t smem = tile * per_token;
     // 16-byte loads: no padding behind D, and every row of q, k and the decays starts on a 16-byte boundary
     const int vec = (D % 16 == 0 && row_stride % 8 == 0 && ((uintptr_t)proj % 16) == 0 && ((uintptr_t)decay % 16) == 0) ? 1 : 0;
-    const long long nz = (long long)n_tokens * H * D;
-    if ((nz + 255) / 256 > 2147483647LL) return GESSO_ERR_BAD_SIZE;
-    launch_pdl(gla_decay_kernel, dim3((unsigned)((nz + 255) / 256)), dim3(256), 0, stream, z, z_bias, 1.f / tau, decay,
-               nz, H * D);
+    if ((H * D + 255) / 256 > 65535) return GESSO_ERR_BAD_SIZE;
+    launch_pdl(gla_decay_kernel, dim3((unsigned)n_tokens, (unsigned)((H * D + 255) / 256)), dim3(256), 0, stream, z, z_bias,
+               1.f / tau, decay, H * D);
 #define GO(T, LL, MODE, GRID)                                                                                       \
     launch_pdl(gla_kernel<T, LL, MODE>, GRID, dim3(GLA_THREADS), smem, stream, (const T*)proj, row_stride,          \
                (const float*)decay, q_scale, state, slot_stride, seg_start, slots, tile_seg, tile_q0, ws, ws_decay, out, \
