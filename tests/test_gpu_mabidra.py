@@ -118,7 +118,8 @@ def segments(lens):
 
 
 # ---- mechanisms alone ------------------------------------------------------------------------------------
-@pytest.mark.parametrize("width,groups,rows", [(64, 2, 5), (48, 1, 37), (512, 4, 300), (96, 6, 70), (30, 3, 9), (256, 256, 4)])
+@pytest.mark.parametrize("width,groups,rows", [(64, 2, 5), (48, 1, 37), (512, 4, 300), (96, 6, 70), (30, 3, 9), (256, 256, 4),
+                                               (1024, 4, 33), (2048, 4, 9), (2048, 2, 5), (768, 2, 7)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("delta_dtype", [torch.float32, torch.bfloat16])
 def test_group_norm_of_the_delta_then_of_the_stream(width, groups, rows, out_dtype, delta_dtype):
